@@ -1,0 +1,30 @@
+"""B200-native fp32 GEMM behind the cpp-ai-engine ``Tensor::matmul`` seam.
+
+The product is the C-ABI shared library ``libb200gemm.so`` (CUDA for sm_100a, sources in
+``csrc/``, declarations in ``include/b200_gemm.h``).  This package is the thin Python host
+side: it builds and loads the library and mirrors the reference's operator interface for
+the path (``matmul`` with the engine's batch rules, the two backward forms, and the device
+seam ``cuda::ops::matmul``), using torch only for device memory and streams.
+
+There is no CPU fallback: if the library is missing or no sm_100 device is present, calls
+raise.
+"""
+from __future__ import annotations
+
+from . import build as _build  # noqa: F401
+from .lib import (  # noqa: F401
+    B200Error,
+    PRECISION_3XTF32,
+    PRECISION_TF32,
+    gemm,
+    gemm_colshard,
+    launch_count,
+    lib_path,
+    load,
+    matmul_host,
+    set_option,
+    status,
+    workspace_bytes,
+)
+from . import engine, lib, shard  # noqa: F401
+from .engine import Tensor, matmul, matmul_backward, ops_matmul  # noqa: F401

@@ -1,0 +1,590 @@
+// The fp32-accurate GEMM kernel for sm_100a.
+//
+//   C[b] = alpha * op(A[b]) x op(B[b]) + beta * C[b]          (row-major storage, fp32 in/out)
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Inside a CTA:
+//
+//   warp 0      TMA producer   one lane issues cp.async.bulk.tensor loads of the raw fp32
+//                              A/B tiles of a k-block (BK = 32 or 16 values of k) into a
+//                              shared-memory stage; transposed operands are loaded in their
+//                              stored orientation and described to the tensor core as
+//                              MN-major, so no transpose is ever materialised.
+//   warps 4..11 workers        split every fp32 value of the stage IN PLACE into its TF32
+//                              head (written back over the raw value) and TF32 tail (written
+//                              to the second half of the stage).  The split is layout-blind:
+//                              it never needs to know the swizzle or the orientation.
+//                              The same warps later drain the TMEM accumulator.
+//   warp 1      MMA issuer     one lane issues, per 8 values of k, three tcgen05.mma
+//                              kind::tf32 products (tail x head, head x tail, head x head)
+//                              into a TMEM accumulator, and commits to mbarriers.
+//
+// The tensor core's fp32 accumulator truncates: a chain of thousands of MMAs into one TMEM
+// accumulator drifts (measured 2.9e-5 relative at K = 2048).  So the chain is cut every
+// `promote_every` k-blocks: the MMA warp switches to the second TMEM accumulator while the
+// workers pull the finished partial tile with tcgen05.ld and add it to fp32 registers with
+// ordinary round-to-nearest adds.  The epilogue then writes alpha * acc + beta * C from
+// registers.
+//
+// When an operand cannot be described to TMA (base not 16-byte aligned, leading dimension not a
+// multiple of 4 floats: K = 9 im2col, N = 121 / 10 heads) the workers load it with plain
+// global loads, split in registers and store straight into the K-major swizzled layout; the
+// TMA warp idles.  Same MMA and epilogue code.
+//
+// Every wait is bounded (see sm100_ptx.cuh).  A wait that runs out records a bit in
+// *status, raises a CTA-wide abort flag that all other waits poll, and every role falls
+// through to the common exit where TMEM is released.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int kBM = 128;          // tile rows = MMA M
+constexpr int kWorkerWarps = 8;   // split + promote + epilogue
+constexpr int kWorkerThreads = kWorkerWarps * 32;
+constexpr int kFirstWorkerWarp = 4;  // warps 0..3 form the control warpgroup (two of them idle)
+constexpr int kThreads = kFirstWorkerWarp * 32 + kWorkerThreads;
+constexpr int kMaxDest = 8;
+
+// status bits (device-side wait that ran out, by role)
+constexpr int kStatProducer = 1;
+constexpr int kStatMma = 2;
+constexpr int kStatWorkerFull = 4;
+constexpr int kStatWorkerAcc = 8;
+
+struct GemmParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, kblocks, split_k, kb_per_split, group_m, total_work;
+    const float* A;
+    const float* B;
+    float* dest[kMaxDest];  // dest[0] = C; further entries receive the same tiles (column-shard gather)
+    int n_dest;
+    long long lda, ldb, ldc, strideA, strideB, strideC;
+    int transA, transB;
+    float alpha, beta;
+    int precision;      // 0 = 3xTF32, 1 = TF32
+    int promote_every;  // k-blocks per TMEM accumulation chain
+    float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
+    int* status;
+    // tensor-core view of the shared-memory tiles
+    uint32_t a_lbo, a_sbo, a_kstep, a_layout;
+    uint32_t b_lbo, b_sbo, b_kstep, b_layout;
+    uint32_t idesc;
+    // loader / epilogue fast paths
+    int a_vec_ok, b_vec_ok, c_vec_ok;
+};
+
+template <int BN, int BK>
+struct TileCfg {
+    static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+    static_assert(BK == 16 || BK == 32, "unsupported k-block");
+    static constexpr uint32_t kABytes = kBM * BK * 4;
+    static constexpr uint32_t kBBytes = BN * BK * 4;
+    static constexpr uint32_t kHalf = kABytes + kBBytes;  // raw / head tiles; tails follow
+    static constexpr uint32_t kStageBytes = 2 * kHalf;
+    static constexpr int kMaxStages = (227 * 1024 - 2048) / kStageBytes;
+    static constexpr int kStages = kMaxStages > 4 ? 4 : kMaxStages;
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;           // two accumulators
+    static constexpr int kCols = BN / 2;                                  // columns per worker
+};
+
+struct Work {
+    int b, mt, nt, sp, kb0, kb1;
+};
+
+__device__ __forceinline__ Work decode_work(const GemmParams& p, int w) {
+    Work r;
+    r.sp = w % p.split_k;
+    int t = w / p.split_k;
+    const int tiles = p.tiles_m * p.tiles_n;
+    r.b = t / tiles;
+    t -= r.b * tiles;
+    // Tiles are walked in bands of group_m tile-rows so that the CTAs running at one time
+    // cover a near-square patch of C and share A and B tiles through L2.
+    const int per_group = p.group_m * p.tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * p.group_m;
+    const int gsize = min(p.tiles_m - first_m, p.group_m);
+    const int in_g = t - g * per_group;
+    r.mt = first_m + in_g % gsize;
+    r.nt = in_g / gsize;
+    r.kb0 = r.sp * p.kb_per_split;
+    r.kb1 = min(p.kblocks, r.kb0 + p.kb_per_split);
+    return r;
+}
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                         int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag) return false;
+        if (global_timer_ns() - start > kWaitBudgetNs) {
+            atomicOr(status, code);
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+// Loads a ROWS x 32 tile of one operand with plain global loads, splits it and stores the
+// head / tail tiles in the K-major 128-byte-swizzled layout.  `k_contig`: k is the contiguous
+// index of the stored matrix (A not transposed, B transposed).
+template <int ROWS>
+__device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, long long ld,
+                                                bool k_contig, bool vec_ok, int row0, int row_max,
+                                                int k0, int K, uint8_t* hi, uint8_t* lo,
+                                                bool want_lo, int wtid) {
+    constexpr int kChunks = 8;  // 16-byte chunks per 128-byte row
+    constexpr int kUnits = ROWS * kChunks;
+    constexpr int kPer = kUnits / kWorkerThreads;
+    static_assert(kUnits % kWorkerThreads == 0, "tile does not divide over the workers");
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        int r, c;
+        if (k_contig) {
+            r = unit / kChunks;
+            c = unit % kChunks;
+        } else {
+            r = unit % ROWS;
+            c = unit / ROWS;
+        }
+        const int gr = row0 + r;
+        const int gk = k0 + c * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gr < row_max && gk < K) {
+            if (k_contig) {
+                const float* src = base + (long long)gr * ld + gk;
+                if (vec_ok && gk + 3 < K) {
+                    x = __ldg(reinterpret_cast<const float4*>(src));
+                } else {
+                    x.x = __ldg(src);
+                    if (gk + 1 < K) x.y = __ldg(src + 1);
+                    if (gk + 2 < K) x.z = __ldg(src + 2);
+                    if (gk + 3 < K) x.w = __ldg(src + 3);
+                }
+            } else {
+                const float* src = base + (long long)gk * ld + gr;
+                x.x = __ldg(src);
+                if (gk + 1 < K) x.y = __ldg(src + ld);
+                if (gk + 2 < K) x.z = __ldg(src + 2 * ld);
+                if (gk + 3 < K) x.w = __ldg(src + 3 * ld);
+            }
+        }
+        v[u] = x;
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        int r, c;
+        if (k_contig) {
+            r = unit / kChunks;
+            c = unit % kChunks;
+        } else {
+            r = unit % ROWS;
+            c = unit / ROWS;
+        }
+        const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
+                             (uint32_t)((c ^ (r & 7)) << 4);
+        float4 h, l;
+        tf32_split(v[u].x, h.x, l.x);
+        tf32_split(v[u].y, h.y, l.y);
+        tf32_split(v[u].z, h.z, l.z);
+        tf32_split(v[u].w, h.w, l.w);
+        *reinterpret_cast<float4*>(hi + off) = h;
+        if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
+    }
+}
+
+template <int BN, int BK, bool kTma>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
+                 const __grid_constant__ CUtensorMap mapB) {
+    using Cfg = TileCfg<BN, BK>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kCols = Cfg::kCols;
+    static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+    __shared__ __align__(8) uint64_t full_bar[kStages];   // TMA bytes landed
+    __shared__ __align__(8) uint64_t split_bar[kStages];  // head/tail tiles ready for the MMA
+    __shared__ __align__(8) uint64_t empty_bar[kStages];  // MMAs reading the stage finished
+    __shared__ __align__(8) uint64_t accf_bar[2];         // accumulator chain finished
+    __shared__ __align__(8) uint64_t acce_bar[2];         // accumulator drained
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&split_bar[s]), kWorkerWarps);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&accf_bar[b]), 1);
+            mbar_init(smem_u32(&acce_bar[b]), kWorkerWarps);
+        }
+        abort_s = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc(smem_u32(&tmem_base_s), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    if (kTma && warp == 0 && lane == 0) {
+        tma_prefetch_desc(&mapA);
+        tma_prefetch_desc(&mapB);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+    const bool prec3 = (p.precision == 0);
+    const int promote_every = p.promote_every;
+
+    // The 128 x 256 tile keeps 128 accumulators per worker thread in registers: hand the
+    // control warpgroup's registers to the two worker warpgroups.
+    if (warp < kFirstWorkerWarp) {
+      if constexpr (BN == 256) reg_dealloc<40>();
+      if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (kTma && lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+                const Work wk = decode_work(p, w);
+                const int za = p.strideA ? wk.b : 0;
+                const int zb = p.strideB ? wk.b : 0;
+                for (int kb = wk.kb0; kb < wk.kb1; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
+                                  kStatProducer)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&full_bar[s]);
+                    const uint32_t sa = smem_u32(smem) + s * Cfg::kStageBytes;
+                    const uint32_t sb = sa + Cfg::kABytes;
+                    mbar_arrive_expect_tx(full, Cfg::kHalf);
+                    if (!p.transA) {
+                        tma_load_3d(sa, &mapA, full, kb * BK, wk.mt * kBM, za);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kBM / 32; ++j)
+                            tma_load_3d(sa + j * (BK * 128), &mapA, full, wk.mt * kBM + j * 32,
+                                        kb * BK, za);
+                    }
+                    if (p.transB) {
+                        tma_load_3d(sb, &mapB, full, kb * BK, wk.nt * BN, zb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 32; ++j)
+                            tma_load_3d(sb + j * (BK * 128), &mapB, full, wk.nt * BN + j * 32,
+                                        kb * BK, zb);
+                    }
+                }
+            }
+            if (!ok) {
+                // Leave no bulk copy in flight behind an exiting CTA: give the loads already
+                // issued a short while to land.
+                for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
+                    const uint32_t j = it - back;
+                    mbar_wait(smem_u32(&full_bar[j % kStages]), (j / kStages) & 1, 20000000ull);
+                }
+            }
+        }
+      } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t s0 = smem_u32(smem);
+            const uint64_t dA_hi = make_smem_desc(s0, p.a_lbo, p.a_sbo, p.a_layout);
+            const uint64_t dB_hi = make_smem_desc(s0 + Cfg::kABytes, p.b_lbo, p.b_sbo, p.b_layout);
+            const uint32_t ka = p.a_kstep >> 4, kb_step = p.b_kstep >> 4;
+            constexpr uint32_t kLoOff = Cfg::kHalf >> 4;
+            const uint32_t idesc = p.idesc;
+            uint32_t it = 0, chain = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+                const Work wk = decode_work(p, w);
+                const int nkb = wk.kb1 - wk.kb0;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    const bool chain_start = (i % promote_every) == 0;
+                    const bool chain_end = ((i + 1) % promote_every) == 0 || i == nkb - 1;
+                    const uint32_t buf = chain & 1;
+                    if (chain_start) {
+                        if (!wait_bar(smem_u32(&acce_bar[buf]), ((chain >> 1) & 1) ^ 1, abort_flag,
+                                      p.status, kStatMma)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!wait_bar(smem_u32(&split_bar[s]), ph, abort_flag, p.status, kStatMma)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t d = tmem + buf * BN;
+                    const uint32_t soff = (s * Cfg::kStageBytes) >> 4;
+                    uint32_t accumulate = chain_start ? 0u : 1u;
+                    if (prec3) {
+                        // The accumulator truncates after every MMA, by an amount relative to
+                        // its magnitude.  The two correction products are ~2^-11 of the head
+                        // product: issue all of them first, while the accumulator is still
+                        // tiny, so that only the BK/8 head products truncate at full scale.
+#pragma unroll
+                        for (int ks = 0; ks < BK / 8; ++ks) {
+                            const uint64_t ah = dA_hi + (soff + ks * ka);
+                            const uint64_t bh = dB_hi + (soff + ks * kb_step);
+                            mma_tf32_ss(d, ah + kLoOff, bh, idesc, accumulate);
+                            mma_tf32_ss(d, ah, bh + kLoOff, idesc, 1u);
+                            accumulate = 1u;
+                        }
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < BK / 8; ++ks) {
+                        const uint64_t ah = dA_hi + (soff + ks * ka);
+                        const uint64_t bh = dB_hi + (soff + ks * kb_step);
+                        mma_tf32_ss(d, ah, bh, idesc, accumulate);
+                        accumulate = 1u;
+                    }
+                    tc_commit(smem_u32(&empty_bar[s]));
+                    if (chain_end) {
+                        tc_commit(smem_u32(&accf_bar[buf]));
+                        ++chain;
+                    }
+                }
+            }
+        }
+      }
+    } else {
+        // ------------------------------------------------------------------ workers
+        if constexpr (BN == 256) reg_alloc<232>();
+        const int wid = warp - kFirstWorkerWarp;
+        const int wtid = threadIdx.x - kFirstWorkerWarp * 32;
+        const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*quarter .. +31
+        const int half = wid >> 2;     // which half of the tile's columns
+        float acc[kCols];
+        uint32_t it = 0, chain = 0;
+        bool ok = true;
+
+        // Adds the finished TMEM partial of accumulator chain `c` into the fp32 registers.
+        auto promote = [&](uint32_t c) -> bool {
+            const uint32_t buf = c & 1;
+            bool got = wait_bar(smem_u32(&accf_bar[buf]), (c >> 1) & 1, abort_flag, p.status,
+                                kStatWorkerAcc);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) return false;
+            tc_fence_after_sync();
+            const uint32_t t0 = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN +
+                                half * kCols;
+            if constexpr (kCols >= 32) {
+#pragma unroll
+                for (int g = 0; g < kCols / 32; ++g) {
+                    uint32_t v[32];
+                    tmem_ld_x32(t0 + g * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[g * 32 + j] += __uint_as_float(v[j]);
+                }
+            } else {
+                uint32_t v[16];
+                tmem_ld_x16(t0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(v[j]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acce_bar[buf]));
+            return true;
+        };
+
+        for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+            const Work wk = decode_work(p, w);
+            const int nkb = wk.kb1 - wk.kb0;
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+
+            for (int i = 0; i < nkb && ok; ++i, ++it) {
+                const uint32_t s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1;
+                uint8_t* stage = smem + s * Cfg::kStageBytes;
+                if constexpr (kTma) {
+                    bool got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                                        kStatWorkerFull);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) {
+                        ok = false;
+                        break;
+                    }
+                    float4* hi = reinterpret_cast<float4*>(stage);
+                    float4* lo = reinterpret_cast<float4*>(stage + Cfg::kHalf);
+                    constexpr int kN4 = Cfg::kHalf / 16;
+#pragma unroll 4
+                    for (int q = wtid; q < kN4; q += kWorkerThreads) {
+                        const float4 x = hi[q];
+                        float4 h, l;
+                        tf32_split(x.x, h.x, l.x);
+                        tf32_split(x.y, h.y, l.y);
+                        tf32_split(x.z, h.z, l.z);
+                        tf32_split(x.w, h.w, l.w);
+                        hi[q] = h;
+                        if (prec3) lo[q] = l;
+                    }
+                } else {
+                    bool got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
+                                        kStatWorkerFull);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) {
+                        ok = false;
+                        break;
+                    }
+                    const int k0 = (wk.kb0 + i) * BK;
+                    const float* a_base = p.A + (long long)wk.b * p.strideA;
+                    const float* b_base = p.B + (long long)wk.b * p.strideB;
+                    ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
+                                         p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
+                    ldg_split_store<BN>(b_base, p.ldb, p.transB != 0, p.b_vec_ok != 0, wk.nt * BN,
+                                        p.N, k0, p.K, stage + Cfg::kABytes,
+                                        stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
+                }
+                // generic-proxy writes -> visible to the tensor core's async-proxy reads
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&split_bar[s]));
+
+                // Drain the chain that ended one k-block ago (its MMAs have had a whole
+                // k-block of time to finish, so this rarely waits).
+                if (i >= 1 && ((i % promote_every) == 0)) {
+                    if (!promote(chain)) {
+                        ok = false;
+                        break;
+                    }
+                    ++chain;
+                }
+            }
+            if (!ok) break;
+            if (!promote(chain)) {  // the last chain of the tile
+                ok = false;
+                break;
+            }
+            ++chain;
+
+            // ---------------------------------------------------------------- epilogue
+            const int row = wk.mt * kBM + quarter * 32 + lane;
+            const int col0 = wk.nt * BN + half * kCols;
+            if (row < p.M && col0 < p.N) {
+                if (p.split_k > 1) {
+                    float* crow = p.partial +
+                                  (((long long)wk.sp * p.batch + wk.b) * p.M + row) * (long long)p.N;
+                    const bool vec = (p.N & 3) == 0;
+#pragma unroll
+                    for (int j = 0; j < kCols; j += 4) {
+                        const int col = col0 + j;
+                        if (vec && col + 3 < p.N) {
+                            *reinterpret_cast<float4*>(crow + col) =
+                                make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < p.N) crow[col + e] = acc[j + e];
+                        }
+                    }
+                } else {
+                    const float alpha = p.alpha, beta = p.beta;
+                    const long long coff = (long long)wk.b * p.strideC + (long long)row * p.ldc;
+                    const bool vec = p.c_vec_ok != 0;
+                    for (int dd = 0; dd < p.n_dest; ++dd) {
+                        float* crow = p.dest[dd] + coff;
+#pragma unroll
+                        for (int j = 0; j < kCols; j += 4) {
+                            const int col = col0 + j;
+                            if (vec && col + 3 < p.N) {
+                                float4 o = make_float4(alpha * acc[j], alpha * acc[j + 1],
+                                                       alpha * acc[j + 2], alpha * acc[j + 3]);
+                                if (beta != 0.f) {
+                                    const float4 old = *reinterpret_cast<const float4*>(crow + col);
+                                    o.x += beta * old.x;
+                                    o.y += beta * old.y;
+                                    o.z += beta * old.z;
+                                    o.w += beta * old.w;
+                                }
+                                *reinterpret_cast<float4*>(crow + col) = o;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    if (col + e < p.N) {
+                                        float o = alpha * acc[j + e];
+                                        if (beta != 0.f) o += beta * crow[col + e];
+                                        crow[col + e] = o;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+// C = alpha * sum_s partial[s] + beta * C, splits added in ascending order so the result does
+// not depend on scheduling.  One thread per output element.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ C,
+                                     int split, long long batch, long long M, long long N,
+                                     long long ldc, long long strideC, float alpha, float beta) {
+    const long long total = batch * M * N;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        float s = 0.f;
+        for (int k = 0; k < split; ++k) s += partial[(long long)k * total + i];
+        const long long b = i / (M * N);
+        const long long r = (i - b * M * N) / N;
+        const long long c = i - b * M * N - r * N;
+        float* out = C + b * strideC + r * ldc + c;
+        float o = alpha * s;
+        if (beta != 0.f) o += beta * *out;
+        *out = o;
+    }
+}
+
+// K == 0: the product is empty, C = beta * C.
+__global__ void scale_c_kernel(float* __restrict__ C, long long batch, long long M, long long N,
+                               long long ldc, long long strideC, float beta) {
+    const long long total = batch * M * N;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const long long b = i / (M * N);
+        const long long r = (i - b * M * N) / N;
+        const long long c = i - b * M * N - r * N;
+        float* out = C + b * strideC + r * ldc + c;
+        *out = (beta == 0.f) ? 0.f : beta * *out;
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,545 @@
+// Host side of the B200 GEMM library: argument checks, tile / loader / split-K selection,
+// TMA tensor-map encoding, launches, and the extern "C" surface declared in
+// include/b200_gemm.h.  No CPU fallback exists: a shape the kernels cannot run is an error.
+#include "../../include/b200_gemm.h"
+#include "gemm_kernel.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status = nullptr;  // device status word of the bounded waits
+    // staging for the *_host entry point (grow-only)
+    float* stage_a = nullptr;
+    float* stage_b = nullptr;
+    float* stage_c = nullptr;
+    void* stage_ws = nullptr;
+    size_t cap_a = 0, cap_b = 0, cap_c = 0, cap_ws = 0;
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+std::atomic<uint64_t> g_launches{0};
+
+struct Options {
+    long tile_n = 0;
+    long split_k = 0;
+    long promote_every = 1;
+    long force_ldg = 0;
+    long k_block = 32;
+};
+Options g_opt;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// Resolves the driver's tensor-map encoder at run time so the library itself does not link
+// against libcuda and still loads on a machine without a driver.
+int resolve_encoder() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess) {
+        cudaGetLastError();
+        return B200_EDEVICE;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return 0;
+}
+
+int device_state(DeviceState** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return B200_EDEVICE;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        int major = 0, sms = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+            return static_cast<int>(e);
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+            return static_cast<int>(e);
+        if (major != 10) return B200_EDEVICE;  // tcgen05 / TMEM exist on sm_100 only
+        if ((e = cudaMalloc(&st.status, sizeof(int))) != cudaSuccess) return static_cast<int>(e);
+        if ((e = cudaMemset(st.status, 0, sizeof(int))) != cudaSuccess) return static_cast<int>(e);
+        st.cc_major = major;
+        st.sm_count = sms;
+        st.ready = true;
+    }
+    *out = &st;
+    return 0;
+}
+
+struct OperandMap {
+    CUtensorMap map;
+    uint32_t lbo, sbo, kstep, layout;
+};
+
+// Describes one operand tile to TMA (how to fetch it) and to the tensor core (how it lies in
+// shared memory afterwards).
+//   k_contig: k is the contiguous index of the stored matrix -> K-major tile: one box of
+//             `rows` x BK, rows of BK*4 bytes, swizzle = row width (128 B or 64 B).
+//   else      the m / n index is contiguous -> MN-major tile: boxes of 32 (m|n) x BK (k),
+//             128-byte rows with 32-byte swizzle atoms, the only MN-major layout the tensor
+//             core accepts for 32-bit operands.
+int make_operand_map(OperandMap* om, const float* base, bool k_contig, int64_t rows_total,
+                     int64_t K, int64_t ld, int64_t batch_stride, int64_t batch, int tile_rows,
+                     int bk) {
+    cuuint64_t dims[3];
+    cuuint64_t strides[2];
+    cuuint32_t box[3];
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    CUtensorMapSwizzle swz;
+    const int64_t nbatch = batch_stride ? batch : 1;
+    if (k_contig) {
+        dims[0] = static_cast<cuuint64_t>(K);
+        dims[1] = static_cast<cuuint64_t>(rows_total);
+        box[0] = bk;
+        box[1] = tile_rows;
+        swz = (bk == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+        om->layout = (bk == 32) ? kLayoutSw128 : kLayoutSw64;
+        om->lbo = 16;
+        om->sbo = 8u * bk * 4u;  // eight rows
+        om->kstep = 32;          // 8 floats along the row
+    } else {
+        dims[0] = static_cast<cuuint64_t>(rows_total);
+        dims[1] = static_cast<cuuint64_t>(K);
+        box[0] = 32;
+        box[1] = bk;
+        swz = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+        om->layout = 1;           // 128-byte swizzle with 32-byte atoms
+        om->lbo = bk * 128u;      // next 32 m|n: next box
+        om->sbo = 512;            // next 4 k: four 128-byte rows
+        om->kstep = 1024;         // 8 k
+    }
+    dims[2] = static_cast<cuuint64_t>(nbatch);
+    box[2] = 1;
+    strides[0] = static_cast<cuuint64_t>(ld) * 4u;
+    const int64_t outer_rows = k_contig ? rows_total : K;
+    const int64_t bs = batch_stride ? batch_stride : ld * outer_rows;
+    strides[1] = static_cast<cuuint64_t>(bs) * 4u;
+    if (strides[1] == 0) strides[1] = 16;
+    CUresult r = g_encode(&om->map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                          const_cast<float*>(base), dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : B200_EINVAL;
+}
+
+bool tma_legal(const float* base, int64_t ld, int64_t batch_stride, int64_t batch) {
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+    if (ld & 3) return false;
+    if (batch > 1 && batch_stride != 0 && (batch_stride & 3)) return false;
+    if (ld * 4 >= (1ll << 40) || batch_stride * 4 >= (1ll << 40)) return false;
+    return true;
+}
+
+template <int BN, int BK, bool kTma>
+int launch_cfg(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mb, int grid,
+               cudaStream_t stream) {
+    using Cfg = TileCfg<BN, BK>;
+    static bool attr_set[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, BK, kTma>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(Cfg::kSmemBytes));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_set[dev] = true;
+    }
+    gemm_tf32_kernel<BN, BK, kTma><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p, ma, mb);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& ma,
+             const CUtensorMap& mb, int grid, cudaStream_t stream) {
+#define B200_CASE(BN_)                                                                     \
+    case BN_:                                                                              \
+        if (!tma) return launch_cfg<BN_, 32, false>(p, ma, mb, grid, stream);              \
+        if (bk == 16) return launch_cfg<BN_, 16, true>(p, ma, mb, grid, stream);           \
+        return launch_cfg<BN_, 32, true>(p, ma, mb, grid, stream);
+    switch (bn) {
+        B200_CASE(32)
+        B200_CASE(64)
+        B200_CASE(128)
+        B200_CASE(256)
+        default:
+            return B200_EINVAL;
+    }
+#undef B200_CASE
+}
+
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+struct Plan {
+    int bn, bk, split_k, kb_per_split, kblocks, tiles_m, tiles_n;
+    bool tma;
+};
+
+Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64_t K, bool tma_ok,
+               size_t workspace_bytes) {
+    Plan pl{};
+    pl.tma = tma_ok && !g_opt.force_ldg;
+    pl.bk = (pl.tma && g_opt.k_block == 16) ? 16 : 32;
+    pl.tiles_m = ceil_div(M, kBM);
+    const int sms = st.sm_count > 0 ? st.sm_count : 148;
+    int bn = 32;
+    if (g_opt.tile_n == 32 || g_opt.tile_n == 64 || g_opt.tile_n == 128 || g_opt.tile_n == 256) {
+        bn = static_cast<int>(g_opt.tile_n);
+    } else {
+        // Score = tensor-core rate of the tile width (wider MMAs amortise the A-operand reads,
+        // measured 1 : 0.68 : 0.4 : 0.22) x how full the last wave of tiles is.  Narrow
+        // products get narrow tiles instead of padding (N = 8, 10, 16, 24 run 32 wide).
+        const int cand[4] = {256, 128, 64, 32};
+        const double rate[4] = {1.0, 0.68, 0.40, 0.22};
+        double best = -1.0;
+        for (int i = 0; i < 4; ++i) {
+            const int c = cand[i];
+            if (c > 32 && N <= c / 2) continue;  // more than half the tile would be padding
+            const int64_t tiles = batch * pl.tiles_m * static_cast<int64_t>(ceil_div(N, c));
+            const int64_t waves = (tiles + sms - 1) / sms;
+            const double useful = static_cast<double>(N) / (static_cast<double>(ceil_div(N, c)) * c);
+            const double score = rate[i] * useful * static_cast<double>(tiles) /
+                                 static_cast<double>(waves * sms);
+            if (score > best) {
+                best = score;
+                bn = c;
+            }
+        }
+    }
+    pl.bn = bn;
+    pl.tiles_n = ceil_div(N, bn);
+    pl.kblocks = ceil_div(K, pl.bk);
+    // Deterministic split-K for tall-skinny products (few output tiles, long K).
+    pl.split_k = 1;
+    pl.kb_per_split = pl.kblocks;
+    const int64_t tiles = batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n);
+    int want = 1;
+    if (g_opt.split_k > 1) {
+        want = static_cast<int>(g_opt.split_k);
+    } else if (g_opt.split_k == 0 && tiles * 2 <= sms && pl.kblocks >= 8) {
+        want = static_cast<int>(sms / tiles);
+        if (want > pl.kblocks / 4) want = pl.kblocks / 4;
+    }
+    if (want > pl.kblocks) want = pl.kblocks;
+    if (want > 1) {
+        const int per = ceil_div(pl.kblocks, want);
+        const int split = ceil_div(pl.kblocks, per);
+        const size_t need = static_cast<size_t>(split) * batch * M * N * sizeof(float);
+        if (split > 1 && workspace_bytes >= need) {
+            pl.split_k = split;
+            pl.kb_per_split = per;
+        }
+    }
+    return pl;
+}
+
+int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* dest, int n_dest,
+              int64_t batch, int64_t M, int64_t N, int64_t K, int transA, int transB, int64_t lda,
+              int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB, int64_t strideC,
+              float alpha, float beta, int precision, void* workspace, size_t workspace_bytes,
+              cudaStream_t stream) {
+    if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
+    if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (n_dest < 1 || n_dest > kMaxDest || dest == nullptr) return B200_EINVAL;
+    if (batch == 0 || M == 0 || N == 0) return B200_OK;
+    for (int i = 0; i < n_dest; ++i)
+        if (dest[i] == nullptr) return B200_EINVAL;
+    if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll || batch > 0x7fffffffll)
+        return B200_ERANGE;
+    if (ldc < N || strideC < 0 || strideA < 0 || strideB < 0) return B200_EINVAL;
+    if (batch > 1 && strideC < M * ldc && strideC != 0) return B200_EINVAL;
+    if (batch > 1 && strideC == 0) return B200_EINVAL;  // every batch would write the same C
+    float* C = dest[0];
+    if (K == 0) {
+        for (int i = 0; i < n_dest; ++i) {
+            scale_c_kernel<<<st.sm_count * 4, 256, 0, stream>>>(dest[i], batch, M, N, ldc, strideC,
+                                                                beta);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+        }
+        return static_cast<int>(cudaGetLastError());
+    }
+    if (A == nullptr || B == nullptr) return B200_EINVAL;
+    if (lda < (transA ? M : K) || ldb < (transB ? K : N)) return B200_EINVAL;
+
+    const bool tma_ok = tma_legal(A, lda, strideA, batch) && tma_legal(B, ldb, strideB, batch);
+    const bool can_split = (n_dest == 1);
+    Plan pl = make_plan(st, batch, M, N, K, tma_ok,
+                        (can_split && workspace != nullptr &&
+                         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0)
+                            ? workspace_bytes
+                            : 0);
+    const int64_t total = batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n) * pl.split_k;
+    if (total > 0x7fffffffll) return B200_ERANGE;
+
+    GemmParams p{};
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.K = static_cast<int>(K);
+    p.batch = static_cast<int>(batch);
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
+    p.kblocks = pl.kblocks;
+    p.split_k = pl.split_k;
+    p.kb_per_split = pl.kb_per_split;
+    p.group_m = 16;
+    p.total_work = static_cast<int>(total);
+    p.A = A;
+    p.B = B;
+    for (int i = 0; i < n_dest; ++i) p.dest[i] = dest[i];
+    p.n_dest = n_dest;
+    p.lda = lda;
+    p.ldb = ldb;
+    p.ldc = ldc;
+    p.strideA = strideA;
+    p.strideB = strideB;
+    p.strideC = strideC;
+    p.transA = transA ? 1 : 0;
+    p.transB = transB ? 1 : 0;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.precision = precision;
+    p.promote_every = g_opt.promote_every >= 1 ? static_cast<int>(g_opt.promote_every) : 1;
+    p.partial = static_cast<float*>(workspace);
+    p.status = st.status;
+    p.a_vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (lda & 3) == 0 &&
+                  (strideA & 3) == 0)
+                     ? 1
+                     : 0;
+    p.b_vec_ok = ((reinterpret_cast<uintptr_t>(B) & 15u) == 0 && (ldb & 3) == 0 &&
+                  (strideB & 3) == 0)
+                     ? 1
+                     : 0;
+    p.c_vec_ok = ((ldc & 3) == 0 && (strideC & 3) == 0) ? 1 : 0;
+    for (int i = 0; i < n_dest; ++i)
+        if (reinterpret_cast<uintptr_t>(dest[i]) & 15u) p.c_vec_ok = 0;
+
+    OperandMap oa{}, ob{};
+    const bool a_k_contig = !transA;  // A stored M x K
+    const bool b_k_contig = transB;   // B stored N x K
+    if (pl.tma) {
+        int rc = resolve_encoder();
+        if (rc) return rc;
+        rc = make_operand_map(&oa, A, a_k_contig, M, K, lda, strideA, batch, kBM, pl.bk);
+        if (rc) return rc;
+        rc = make_operand_map(&ob, B, b_k_contig, N, K, ldb, strideB, batch, pl.bn, pl.bk);
+        if (rc) return rc;
+        p.a_lbo = oa.lbo;
+        p.a_sbo = oa.sbo;
+        p.a_kstep = oa.kstep;
+        p.a_layout = oa.layout;
+        p.b_lbo = ob.lbo;
+        p.b_sbo = ob.sbo;
+        p.b_kstep = ob.kstep;
+        p.b_layout = ob.layout;
+        p.idesc = make_idesc_tf32(kBM, pl.bn, a_k_contig ? 0 : 1, b_k_contig ? 0 : 1);
+    } else {
+        // the register-staged loader always writes K-major 128-byte-swizzled tiles
+        p.a_lbo = p.b_lbo = 16;
+        p.a_sbo = p.b_sbo = 1024;
+        p.a_kstep = p.b_kstep = 32;
+        p.a_layout = p.b_layout = kLayoutSw128;
+        p.idesc = make_idesc_tf32(kBM, pl.bn, 0, 0);
+    }
+
+    const int grid = static_cast<int>(total < st.sm_count ? total : st.sm_count);
+    int rc = dispatch(pl.bn, pl.bk, pl.tma, p, oa.map, ob.map, grid, stream);
+    if (rc) return rc;
+    if (pl.split_k > 1) {
+        const int64_t elems = batch * M * N;
+        int blocks = static_cast<int>((elems + 255) / 256);
+        if (blocks > st.sm_count * 8) blocks = st.sm_count * 8;
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(workspace), C,
+                                                         pl.split_k, batch, M, N, ldc, strideC,
+                                                         alpha, beta);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        rc = static_cast<int>(cudaGetLastError());
+    }
+    return rc;
+}
+
+int grow(void** ptr, size_t* cap, size_t need) {
+    if (need <= *cap) return 0;
+    if (*ptr) cudaFree(*ptr);
+    *ptr = nullptr;
+    *cap = 0;
+    cudaError_t e = cudaMalloc(ptr, need);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    *cap = need;
+    return 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+                  int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
+                  int64_t strideA, int64_t strideB, int64_t strideC, float alpha, float beta,
+                  int precision, void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    float* dest[1] = {C};
+    if (C == nullptr) return B200_EINVAL;
+    if (batch == 1 && strideC == 0) strideC = M * ldc;
+    return gemm_impl(*st, A, B, dest, 1, batch, M, N, K, transA, transB, lda, ldb, ldc, strideA,
+                     strideB, strideC, alpha, beta, precision, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K) {
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+    DeviceState tmp;
+    DeviceState* st = nullptr;
+    if (device_state(&st) != 0) {
+        tmp.sm_count = 148;
+        st = &tmp;
+    }
+    Plan pl = make_plan(*st, batch, M, N, K, true, static_cast<size_t>(-1));
+    if (pl.split_k <= 1) return 0;
+    return static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float);
+}
+
+int b200_matmul_f32(const float* a, const float* b, float* out, size_t batch, size_t rows,
+                    size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+    const int64_t M = static_cast<int64_t>(rows), K = static_cast<int64_t>(inner_dim),
+                  N = static_cast<int64_t>(cols), nb = static_cast<int64_t>(batch);
+    return b200_gemm_f32(a, b, out, nb, M, N, K, 0, 0, K, N, N, a_batched ? M * K : 0,
+                         b_batched ? K * N : 0, M * N, 1.0f, beta, B200_PRECISION_3XTF32, workspace,
+                         workspace_bytes, stream);
+}
+
+int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batch, size_t rows,
+                         size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (a == nullptr || b == nullptr || out == nullptr) return B200_EINVAL;
+    const size_t na = (a_batched ? batch : 1) * rows * inner_dim * sizeof(float);
+    const size_t nb = (b_batched ? batch : 1) * inner_dim * cols * sizeof(float);
+    const size_t nc = batch * rows * cols * sizeof(float);
+    if (nc == 0) return B200_OK;
+    const size_t nws = b200_gemm_f32_workspace(static_cast<int64_t>(batch), static_cast<int64_t>(rows),
+                                               static_cast<int64_t>(cols),
+                                               static_cast<int64_t>(inner_dim));
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if ((rc = grow(reinterpret_cast<void**>(&st->stage_a), &st->cap_a, na ? na : 16))) return rc;
+        if ((rc = grow(reinterpret_cast<void**>(&st->stage_b), &st->cap_b, nb ? nb : 16))) return rc;
+        if ((rc = grow(reinterpret_cast<void**>(&st->stage_c), &st->cap_c, nc))) return rc;
+        if (nws && (rc = grow(&st->stage_ws, &st->cap_ws, nws))) return rc;
+    }
+    cudaStream_t stream = nullptr;
+    cudaError_t e;
+    if (na && (e = cudaMemcpyAsync(st->stage_a, a, na, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return static_cast<int>(e);
+    if (nb && (e = cudaMemcpyAsync(st->stage_b, b, nb, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return static_cast<int>(e);
+    if (beta != 0.0f &&
+        (e = cudaMemcpyAsync(st->stage_c, out, nc, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return static_cast<int>(e);
+    rc = b200_matmul_f32(st->stage_a, st->stage_b, st->stage_c, batch, rows, inner_dim, cols,
+                         a_batched, b_batched, beta, nws ? st->stage_ws : nullptr, nws, stream);
+    if (rc) return rc;
+    if ((e = cudaMemcpyAsync(out, st->stage_c, nc, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
+        return static_cast<int>(e);
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
+    return B200_OK;
+}
+
+int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,
+                           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t cols, int64_t lda,
+                           int64_t ldb, int64_t ldc, int precision, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (dest == nullptr || n_dest < 1 || n_dest > kMaxDest) return B200_EINVAL;
+    if (col0 < 0 || cols < 0 || col0 + cols > N || ldb < N || ldc < N) return B200_EINVAL;
+    float* shifted[kMaxDest];
+    for (int i = 0; i < n_dest; ++i) {
+        if (dest[i] == nullptr) return B200_EINVAL;
+        shifted[i] = dest[i] + col0;
+    }
+    return gemm_impl(*st, A, B ? B + col0 : nullptr, shifted, n_dest, 1, M, cols, K, 0, 0, lda, ldb,
+                     ldc, 0, 0, M * ldc, 1.0f, 0.0f, precision, nullptr, 0,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_status(void) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int word = 0;
+    if ((e = cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return static_cast<int>(e);
+    if (word != 0) {
+        cudaMemset(st->status, 0, sizeof(int));
+        return B200_ETIMEDOUT;
+    }
+    return B200_OK;
+}
+
+uint64_t b200_gemm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200_gemm_set_option(const char* name, long value) {
+    if (name == nullptr) return B200_EINVAL;
+    if (!std::strcmp(name, "tile_n")) {
+        if (value != 0 && value != 32 && value != 64 && value != 128 && value != 256)
+            return B200_EINVAL;
+        g_opt.tile_n = value;
+    } else if (!std::strcmp(name, "split_k")) {
+        if (value < 0) return B200_EINVAL;
+        g_opt.split_k = value;
+    } else if (!std::strcmp(name, "promote_every")) {
+        if (value < 1) return B200_EINVAL;
+        g_opt.promote_every = value;
+    } else if (!std::strcmp(name, "force_ldg")) {
+        g_opt.force_ldg = value ? 1 : 0;
+    } else if (!std::strcmp(name, "k_block")) {
+        if (value != 16 && value != 32) return B200_EINVAL;
+        g_opt.k_block = value;
+    } else {
+        return B200_EINVAL;
+    }
+    return B200_OK;
+}
+
+const char* b200_gemm_strerror(int code) {
+    switch (code) {
+        case B200_OK: return "success";
+        case B200_EINVAL: return "invalid argument (shape, stride, flag or null pointer)";
+        case B200_ERANGE: return "dimension out of the range the kernels index";
+        case B200_ENOSPACE: return "workspace too small";
+        case B200_EDEVICE: return "no sm_100 device, or the driver lacks cuTensorMapEncodeTiled";
+        case B200_ETIMEDOUT: return "a bounded device-side wait ran out";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error";
+}
+
+}  // extern "C"

@@ -28,6 +28,18 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // ---------------------------------------------------------------------------
+// register re-partitioning between warpgroups (four consecutive, aligned warps)
+// ---------------------------------------------------------------------------
+template <int kRegs>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

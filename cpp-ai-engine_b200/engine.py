@@ -1,0 +1,214 @@
+"""Host-side mirror of the reference engine's matrix-product interface.
+
+Same names, argument meaning and error behaviour as the reference's ``Tensor::matmul``
+(src/tensor_ops.cpp:475-588) and its device seam ``cuda::ops::matmul``
+(include/engine/detail/cuda_ops.hpp:46-47), so parity tests read like the reference's own.
+Storage is a contiguous float32 torch CUDA tensor; every product runs in the sm_100a library
+through its C ABI.  The backward pass calls the transposed forms directly (``dA = dC x B^T``
+as an NT product, ``dB = A^T x dC`` as a TN product) instead of materialising transposes the
+way the reference does (src/tensor_ops.cpp:576, :581); the values are the same products.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+from . import lib as _lib
+
+_ws_cache = {}
+
+
+def _workspace(device, nbytes: int):
+    """Grow-only scratch per device for the split-K path (the reference keeps one scratch
+    buffer the same way, src/cuda/kernels.cu:593-604)."""
+    import torch
+
+    if nbytes <= 0:
+        return None, 0
+    key = (device.type, device.index)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf, nbytes
+
+
+def _check_operand(t, name: str) -> None:
+    import torch
+
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must live on a CUDA device: there is no CPU path")
+    if t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous (row-major, last stride 1)")
+
+
+def _batch_plan(a_shape: Sequence[int], b_shape: Sequence[int]):
+    """The reference's shape rules (src/tensor_ops.cpp:476-503)."""
+    if len(a_shape) < 2 or len(b_shape) < 2:
+        raise ValueError("MatMul requires at least 2 dimensions in both operands.")
+    batch_a, batch_b = list(a_shape[:-2]), list(b_shape[:-2])
+    a_batched, b_batched = bool(batch_a), bool(batch_b)
+    if a_batched and b_batched and batch_a != batch_b:
+        raise ValueError(f"Batched MatMul needs identical batch axes: {tuple(a_shape)} and {tuple(b_shape)}.")
+    batch_dims = batch_a if a_batched else batch_b
+    M, K = a_shape[-2], a_shape[-1]
+    K2, N = b_shape[-2], b_shape[-1]
+    if K != K2:
+        raise ValueError(f"Incompatible dimensions for MatMul: {tuple(a_shape)} and {tuple(b_shape)}.")
+    batch = 1
+    for d in batch_dims:
+        batch *= d
+    return batch_dims, batch, M, K, N, a_batched, b_batched
+
+
+def ops_matmul(a, b, out, batch: int, rows: int, inner_dim: int, cols: int, a_batched: bool,
+               b_batched: bool, beta: float = 0.0, *, precision: int = _lib.PRECISION_3XTF32,
+               stream=None) -> bool:
+    """``out = a x b + beta * out`` — the seam ``cuda::ops::matmul``.  Always returns True:
+    the device does the work or an exception is raised (the reference returns False to send
+    the caller to its CPU loop; there is no such path here)."""
+    ws_bytes = _lib.workspace_bytes(batch, rows, cols, inner_dim)
+    ws, ws_bytes = _workspace(out.device, ws_bytes)
+    _lib.gemm(a, b, out, batch=batch, M=rows, N=cols, K=inner_dim, lda=inner_dim, ldb=cols, ldc=cols,
+              strideA=rows * inner_dim if a_batched else 0,
+              strideB=inner_dim * cols if b_batched else 0, strideC=rows * cols, beta=beta,
+              precision=precision, workspace=ws, workspace_bytes=ws_bytes, stream=stream)
+    return True
+
+
+def matmul(a, b, *, precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """``Tensor::matmul`` on raw torch tensors: (B..., M, K) x (B..., K, N) -> (B..., M, N),
+    or one 2-D operand shared by every matrix of the other's batch."""
+    import torch
+
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    batch_dims, batch, M, K, N, a_batched, b_batched = _batch_plan(a.shape, b.shape)
+    out = torch.empty(list(batch_dims) + [M, N], dtype=torch.float32, device=a.device)
+    if out.numel() == 0:
+        return out
+    ops_matmul(a, b, out, batch, M, K, N, a_batched, b_batched, 0.0, precision=precision,
+               stream=stream)
+    return out
+
+
+def matmul_backward(a, b, grad_out, *, precision: int = _lib.PRECISION_3XTF32, stream=None,
+                    need_a: bool = True, need_b: bool = True):
+    """Gradients of ``C = a.matmul(b)`` for a given ``dC`` (src/tensor_ops.cpp:570-585).
+
+    ``dA = dC x B^T`` (NT) and ``dB = A^T x dC`` (TN).  The gradient of an operand shared
+    across the batch is the sum over the batch: because the shared operand makes the batch
+    just more rows of one product, it is computed as ONE product with the batch folded into
+    the contraction (dB) or the rows (dA), instead of a batched product followed by a sum.
+    """
+    import torch
+
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    _check_operand(grad_out, "grad_out")
+    batch_dims, batch, M, K, N, a_batched, b_batched = _batch_plan(a.shape, b.shape)
+    if list(grad_out.shape) != list(batch_dims) + [M, N]:
+        raise ValueError(f"Gradient shape {tuple(grad_out.shape)} incompatible with the product's "
+                         f"{tuple(list(batch_dims) + [M, N])}.")
+    dA = dB = None
+
+    def run(A_, B_, C_, **kw):
+        ws_bytes = _lib.workspace_bytes(kw["batch"], kw["M"], kw["N"], kw["K"])
+        ws, ws_bytes = _workspace(C_.device, ws_bytes)
+        _lib.gemm(A_, B_, C_, precision=precision, workspace=ws, workspace_bytes=ws_bytes,
+                  stream=stream, **kw)
+
+    if need_a:
+        dA = torch.empty_like(a)
+        if a_batched or batch == 1:
+            # dA[b] = dC[b] (M x N) x B[b]^T, B stored K x N  -> NT form
+            run(grad_out, b, dA, batch=batch, M=M, N=K, K=N, transB=True, lda=N, ldb=N, ldc=K,
+                strideA=M * N, strideB=K * N if b_batched else 0, strideC=M * K)
+        else:
+            # A is shared, B batched: dA = sum_b dC[b] x B[b]^T = [dC_0 | dC_1 | ...] x [B_0 | B_1 | ...]^T.
+            # With row-major storage that is a batched product summed by beta = 1 accumulation
+            # in ascending batch order.
+            for bi in range(batch):
+                run(grad_out[bi] if grad_out.dim() > 2 else grad_out, b[bi], dA, batch=1, M=M, N=K,
+                    K=N, transB=True, lda=N, ldb=N, ldc=K, beta=0.0 if bi == 0 else 1.0)
+    if need_b:
+        dB = torch.empty_like(b)
+        if b_batched or batch == 1:
+            # dB[b] = A[b]^T (A stored M x K) x dC[b]  -> TN form
+            run(a, grad_out, dB, batch=batch, M=K, N=N, K=M, transA=True, lda=K, ldb=N, ldc=N,
+                strideA=M * K if a_batched else 0, strideB=M * N, strideC=K * N)
+        else:
+            # B is shared, A batched: A is (batch*M) x K and dC is (batch*M) x N, both
+            # contiguous, so dB = A_flat^T x dC_flat is one TN product over batch*M rows.
+            run(a, grad_out, dB, batch=1, M=K, N=N, K=batch * M, transA=True, lda=K, ldb=N, ldc=N)
+    return dA, dB
+
+
+class Tensor:
+    """The slice of ``engine::Tensor`` the matrix-product path needs: a value, an optional
+    gradient, ``matmul`` and ``backward`` (include/engine/tensor.hpp:157-198)."""
+
+    def __init__(self, data, requires_grad: bool = False):
+        _check_operand(data, "data")
+        self.data = data
+        self.requires_grad = requires_grad
+        self.grad: Optional["Tensor"] = None
+        self._parents: Tuple["Tensor", ...] = ()
+        self._backward_fn = None
+
+    @property
+    def shape(self) -> List[int]:
+        return list(self.data.shape)
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        out = Tensor(matmul(self.data, other.data), self.requires_grad or other.requires_grad)
+        if out.requires_grad:
+            a, b = self, other
+            out._parents = (a, b)
+
+            def backward_fn(grad_out):
+                dA, dB = matmul_backward(a.data, b.data, grad_out, need_a=a.requires_grad,
+                                         need_b=b.requires_grad)
+                if a.requires_grad:
+                    a.add_grad(dA)
+                if b.requires_grad:
+                    b.add_grad(dB)
+
+            out._backward_fn = backward_fn
+        return out
+
+    def add_grad(self, g) -> None:
+        """First write copies, later writes accumulate (src/tensor.cpp:168-203)."""
+        if not self.requires_grad:
+            return
+        if list(g.shape) != self.shape:
+            raise ValueError(f"Gradient shape {tuple(g.shape)} incompatible with the tensor's "
+                             f"{tuple(self.shape)}.")
+        if self.grad is None:
+            self.grad = Tensor(g.clone())
+        else:
+            self.grad.data += g
+
+    def backward(self, grad_output) -> None:
+        """Reverse sweep over the recorded products (src/autograd.cpp:104-156)."""
+        order, seen = [], set()
+        stack = [(self, False)]
+        while stack:
+            node, done = stack.pop()
+            if done:
+                order.append(node)
+                continue
+            if id(node) in seen:
+                continue
+            seen.add(id(node))
+            stack.append((node, True))
+            for parent in node._parents:
+                stack.append((parent, False))
+        grads = {id(self): grad_output.data if isinstance(grad_output, Tensor) else grad_output}
+        self.add_grad(grads[id(self)])
+        for node in reversed(order):
+            if node._backward_fn is not None and node.grad is not None:
+                node._backward_fn(node.grad.data)

@@ -1,0 +1,118 @@
+/* C ABI of the B200 (sm_100a) fp32 GEMM library — the drop-in for the reference engine's
+ * matrix-product seam.
+ *
+ * The reference funnels every matrix product of the engine (Linear, attention, Conv2d via
+ * im2col, and the autograd backward forms) through Tensor::matmul (src/tensor_ops.cpp:475-588),
+ * which offers the work to one device entry point:
+ *
+ *     bool engine::cuda::ops::matmul(const Storage& a, const Storage& b, Storage& out,
+ *                                    size_t batch, size_t rows, size_t inner_dim, size_t cols,
+ *                                    bool a_batched, bool b_batched, float beta = 0.0f);
+ *                                                   (include/engine/detail/cuda_ops.hpp:46-47,
+ *                                                    implemented in src/cuda/kernels_matmul.cu:761-898)
+ *
+ * This header declares what a binding of that seam calls instead.  Plain pointers and sizes
+ * only; every pointer is a DEVICE pointer unless the function name ends in _host.  Calls are
+ * stream-ordered and never synchronise unless stated.  Return value: 0 on success, a negative
+ * B200_E* code when the arguments were rejected (nothing was launched), a positive value for
+ * a CUDA runtime error (cudaError_t) raised by the launch.
+ *
+ * Arithmetic: inputs and outputs are fp32.  Products run on the tcgen05 tensor cores in TF32
+ * with the error-compensated three-product split ("3xTF32": a = a_hi + a_lo, b = b_hi + b_lo,
+ * a*b ~ a_lo*b_hi + a_hi*b_lo + a_hi*b_hi) and partial sums are promoted to fp32 registers
+ * every few k-steps, so results stay at fp32-level accuracy.  B200_PRECISION_TF32 is the
+ * opt-in single-product mode (about 1e-3 relative error, like the reference's own
+ * MatmulKernel::TensorCore, include/engine/cuda.hpp:153-177) and is never the default.
+ */
+#ifndef B200_GEMM_H
+#define B200_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_PRECISION_3XTF32 0 /* default: fp32-level accuracy */
+#define B200_PRECISION_TF32 1   /* opt-in: one TF32 product per term */
+
+#define B200_OK 0
+#define B200_EINVAL (-1)    /* bad shape, stride, flag or null pointer */
+#define B200_ERANGE (-2)    /* a dimension exceeds what the kernels index (2^31-1 rows/cols, 65535*... ) */
+#define B200_ENOSPACE (-3)  /* workspace required but too small and no fallback possible */
+#define B200_EDEVICE (-4)   /* no sm_100 device / driver entry point missing */
+#define B200_ETIMEDOUT (-5) /* a device-side wait ran out (reported by b200_gemm_status) */
+
+/* General form.  C[b] = alpha * op(A[b]) x op(B[b]) + beta * C[b] for b in [0, batch).
+ * op(A) is M x K, op(B) is K x N, C is M x N; all matrices are row-major as stored:
+ *   transA == 0: A stored M x K, element (i,k) at A[i*lda + k];  transA != 0: stored K x M.
+ *   transB == 0: B stored K x N, element (k,j) at B[k*ldb + j];  transB != 0: stored N x K.
+ * strideX is the element distance between consecutive batch matrices; 0 shares the operand
+ * across the batch (the reference's a_batched / b_batched == false, src/tensor_ops.cpp:514-515).
+ * The transposed forms replace the materialised Tensor::transpose() the reference performs
+ * before its backward products (src/tensor_ops.cpp:576, :581) and in attention / Conv2d
+ * (src/transformer.cpp:293, src/conv.cpp:322).
+ * beta == 0 never reads C (it may hold anything, like Storage::device_write(),
+ * src/storage.cpp:321-332).
+ * workspace: device scratch for the deterministic split-K path (tall-skinny products); may be
+ * NULL / 0, in which case the product runs unsplit.  Its contents need not be preserved.
+ * stream: a cudaStream_t (NULL = the default stream). */
+int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+                  int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
+                  int64_t strideA, int64_t strideB, int64_t strideC, float alpha, float beta,
+                  int precision, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
+ * not split).  Replaces the reference's scratch_buffer for its split-K partials
+ * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */
+size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K);
+
+/* The reference seam itself, argument for argument (include/engine/detail/cuda_ops.hpp:46-47):
+ * out = a x b + beta * out over `batch` contiguous row-major matrices, a is (rows x inner_dim),
+ * b is (inner_dim x cols); an unbatched operand is reused for every batch element. */
+int b200_matmul_f32(const float* a, const float* b, float* out, size_t batch, size_t rows,
+                    size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same product from HOST buffers: uploads a and b, runs the kernel, downloads out, and returns
+ * after the result is on the host — the whole cost a caller holding host tensors pays, as when
+ * the reference's Storage uploads stale operands and a later data() downloads the result
+ * (src/storage.cpp:281-307).  Device staging buffers are cached per device between calls. */
+int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batch, size_t rows,
+                         size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta);
+
+/* N-column-sharded product for large GEMMs on g GPUs of one node (no reference counterpart:
+ * the reference is single-device, src/cuda/runtime.cu:83).  This rank computes columns
+ * [col0, col0 + cols) of C = A x B from its full A (M x K, lda) and the same columns of the full
+ * B (K x N, ldb), and stores every finished tile at the same position of each of the
+ * n_dest row-major M x N buffers in dest[] (host array of DEVICE pointers: this rank's own C
+ * and, for the fused all-gather, the peers' C mapped into this process).  Plain stores over
+ * NVLink; no multicast.  Callers order completion across ranks themselves (a barrier after the
+ * stream is idle). */
+int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,
+                           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t cols, int64_t lda,
+                           int64_t ldb, int64_t ldc, int precision, void* stream);
+
+/* Device-side health of the launches so far on the current device: synchronises the device,
+ * returns 0 or B200_ETIMEDOUT if any bounded wait inside a kernel ran out, and clears the flag. */
+int b200_gemm_status(void);
+
+/* Number of kernels this library has launched in this process (all devices). */
+uint64_t b200_gemm_launch_count(void);
+
+/* Tuning knobs for benchmarking; unknown names return B200_EINVAL.
+ *   "tile_n"        0 = automatic, else 32 / 64 / 128 / 256
+ *   "split_k"       0 = automatic, 1 = never split, n = force n splits (needs workspace)
+ *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
+ *   "force_ldg"     1 = always use the register-staged loader instead of TMA
+ *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path */
+int b200_gemm_set_option(const char* name, long value);
+
+/* Static description of a code, never NULL. */
+const char* b200_gemm_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,178 @@
+"""TEST INFRASTRUCTURE — ctypes binding of the CPU oracle (``liboracle.so``) and, when it has
+been built, of the unmodified reference engine (``_ref/libengine_ref.so``).
+
+Only tests, ``__graft_entry__.smoke()`` and the benchmark's CPU-baseline legs import this
+module; nothing in the product path does.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ORACLE_LIB = HERE / "liboracle.so"
+REF_LIB = HERE / "_ref" / "libengine_ref.so"
+
+_fp = ctypes.POINTER(ctypes.c_float)
+_dp = ctypes.POINTER(ctypes.c_double)
+_sz = ctypes.c_size_t
+
+_oracle: Optional[ctypes.CDLL] = None
+_ref: Optional[ctypes.CDLL] = None
+
+
+def _f32(x: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+def _p(x: np.ndarray):
+    return x.ctypes.data_as(_fp)
+
+
+def oracle() -> ctypes.CDLL:
+    global _oracle
+    if _oracle is None:
+        if not ORACLE_LIB.exists():
+            env = dict(os.environ)
+            env.setdefault("CC", "gcc")
+            subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True, env=env)
+        _oracle = ctypes.CDLL(str(ORACLE_LIB))
+    return _oracle
+
+
+def have_ref() -> bool:
+    return REF_LIB.exists()
+
+
+def ref() -> ctypes.CDLL:
+    """The reference engine itself (CPU build).  Raises if it was not built here."""
+    global _ref
+    if _ref is None:
+        if not REF_LIB.exists():
+            raise RuntimeError("oracle/_ref/libengine_ref.so has not been built (make -C oracle ref)")
+        lib = ctypes.CDLL(str(REF_LIB))
+        lib.ref_matmul_time.restype = ctypes.c_double
+        lib.ref_last_error.restype = ctypes.c_char_p
+        _ref = lib
+    return _ref
+
+
+class _RngState(ctypes.Structure):
+    _fields_ = [("mt", ctypes.c_uint32 * 624), ("idx", ctypes.c_int)]
+
+
+class Rng:
+    """The reference's global generator: ``manual_seed`` then ``Tensor::rand`` / ``randn`` draws
+    in creation order."""
+
+    def __init__(self, seed: int):
+        self._st = _RngState()
+        oracle().oracle_seed(ctypes.byref(self._st), ctypes.c_uint64(seed))
+
+    def rand(self, shape: Sequence[int], lo: float = -1.0, hi: float = 1.0) -> np.ndarray:
+        out = np.empty(shape, dtype=np.float32)
+        oracle().oracle_rand(ctypes.byref(self._st), _p(out), _sz(out.size), ctypes.c_float(lo),
+                             ctypes.c_float(hi))
+        return out
+
+    def randn(self, shape: Sequence[int], mean: float = 0.0, stddev: float = 1.0) -> np.ndarray:
+        out = np.empty(shape, dtype=np.float32)
+        oracle().oracle_randn(ctypes.byref(self._st), _p(out), _sz(out.size), ctypes.c_float(mean),
+                              ctypes.c_float(stddev))
+        return out
+
+
+def _plan(a: np.ndarray, b: np.ndarray):
+    if a.ndim < 2 or b.ndim < 2:
+        raise ValueError("MatMul requires at least 2 dimensions in both operands.")
+    ba, bb = a.shape[:-2], b.shape[:-2]
+    if ba and bb and ba != bb:
+        raise ValueError("Batched MatMul needs identical batch axes")
+    dims = ba if ba else bb
+    if a.shape[-1] != b.shape[-2]:
+        raise ValueError("Incompatible dimensions for MatMul")
+    batch = int(np.prod(dims)) if dims else 1
+    return dims, batch, a.shape[-2], a.shape[-1], b.shape[-1], int(bool(ba)), int(bool(bb))
+
+
+def matmul(a: np.ndarray, b: np.ndarray, threads: int = 0) -> np.ndarray:
+    """``a.matmul(b)`` as the reference's CPU loop computes it."""
+    a, b = _f32(a), _f32(b)
+    dims, batch, M, K, N, ab, bb = _plan(a, b)
+    c = np.empty(tuple(dims) + (M, N), dtype=np.float32)
+    oracle().oracle_matmul_f32(_p(a), _p(b), _p(c), _sz(batch), _sz(M), _sz(K), _sz(N), ab, bb, threads)
+    return c
+
+
+def matmul_nt(a: np.ndarray, b_nk: np.ndarray, threads: int = 0) -> np.ndarray:
+    """``a.matmul(b.transpose())`` with b stored (..., N, K)."""
+    return matmul(a, np.ascontiguousarray(np.swapaxes(_f32(b_nk), -1, -2)), threads)
+
+
+def matmul_tn(a_km: np.ndarray, b: np.ndarray, threads: int = 0) -> np.ndarray:
+    """``a.transpose().matmul(b)`` with a stored (..., K, M)."""
+    return matmul(np.ascontiguousarray(np.swapaxes(_f32(a_km), -1, -2)), b, threads)
+
+
+def matmul_backward(a: np.ndarray, b: np.ndarray, grad_c: np.ndarray, threads: int = 0):
+    a, b, grad_c = _f32(a), _f32(b), _f32(grad_c)
+    dims, batch, M, K, N, ab, bb = _plan(a, b)
+    ga, gb = np.empty_like(a), np.empty_like(b)
+    oracle().oracle_matmul_backward_f32(_p(a), _p(b), _p(grad_c), _p(ga), _p(gb), _sz(batch), _sz(M),
+                                        _sz(K), _sz(N), ab, bb, threads)
+    return ga, gb
+
+
+def matmul_f64(a: np.ndarray, b: np.ndarray, trans_a: bool = False, trans_b: bool = False,
+               threads: int = 0) -> np.ndarray:
+    """2-D product of fp32 inputs accumulated in fp64 (for separating oracle drift from kernel error)."""
+    a, b = _f32(a), _f32(b)
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    c = np.empty((M, N), dtype=np.float64)
+    oracle().oracle_matmul_f64(_p(a), _p(b), c.ctypes.data_as(_dp), _sz(M), _sz(K), _sz(N),
+                               int(trans_a), int(trans_b), _sz(a.shape[1]), _sz(b.shape[1]), threads)
+    return c
+
+
+def scaled_error(got: np.ndarray, want: np.ndarray) -> float:
+    """The reference's parity metric: max |got - want| / max(1, |want|)
+    (tests/test_cuda_parity.cpp:100-102)."""
+    want = want.astype(np.float64)
+    return float(np.max(np.abs(got.astype(np.float64) - want) / np.maximum(1.0, np.abs(want))))
+
+
+def parity_tolerance(K: int) -> float:
+    """The reference's own bound for fp32 kernels against its CPU loop: 1e-5, widened to
+    2K/2^24 for long contractions because the CPU side's sequential fp32 sum drifts with K
+    (tests/test_cuda_parity.cpp:62, 304-315)."""
+    return max(1e-5, 2.0 * K / float(1 << 24))
+
+
+# --- the reference engine itself -------------------------------------------------------------
+
+def ref_matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    a, b = _f32(a), _f32(b)
+    dims, batch, M, K, N, ab, bb = _plan(a, b)
+    c = np.empty(tuple(dims) + (M, N), dtype=np.float32)
+    if ref().ref_matmul(_p(a), _p(b), _p(c), _sz(batch), _sz(M), _sz(K), _sz(N), ab, bb) != 0:
+        raise ValueError(ref().ref_last_error().decode())
+    return c
+
+
+def ref_matmul_time(a: np.ndarray, b: np.ndarray, repeats: int = 1) -> float:
+    a, b = _f32(a), _f32(b)
+    dims, batch, M, K, N, ab, bb = _plan(a, b)
+    t = ref().ref_matmul_time(_p(a), _p(b), _sz(batch), _sz(M), _sz(K), _sz(N), ab, bb, repeats)
+    if t < 0:
+        raise ValueError(ref().ref_last_error().decode())
+    return float(t)
+
+
+def ref_threads() -> int:
+    return int(ref().ref_num_threads())

@@ -1,0 +1,189 @@
+"""Generates the golden vectors under tests/golden/ (run in the build container, where the
+reference tree and the reference CPU build oracle/_ref are present):
+
+    python tests/golden/make_golden.py [--reference /root/reference]
+
+Outputs (small, committed):
+  pytorch_matmul.npz   the reference's own PyTorch golden vectors for its matrix product and
+                       its gradients (tests/fixtures/matmul*.bin, consumed by
+                       tests/test_reference.cpp:99-114), re-encoded as npz.
+  known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
+  reference_runs.npz   outputs of the UNMODIFIED reference engine (oracle/_ref) on seeded
+                       inputs: its random streams, and per configuration a SHA-256 of the full
+                       product plus a strided sample of it.
+
+The fixture container format read here is the reference's documented one
+(include/engine/serialize.hpp:12-31): "CPPAIENG", u32 version, u32 count, then per tensor
+u32 name length, name, u32 ndim, u64 dims, f32 data; little-endian.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import struct
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+
+from oracle import oracle_py as orc  # noqa: E402
+
+
+def read_fixture(path: Path) -> dict:
+    raw = path.read_bytes()
+    if raw[:8] != b"CPPAIENG":
+        raise ValueError(f"{path}: bad signature")
+    version, count = struct.unpack_from("<II", raw, 8)
+    if version != 1:
+        raise ValueError(f"{path}: version {version}")
+    off = 16
+    out = {}
+    for _ in range(count):
+        (nlen,) = struct.unpack_from("<I", raw, off)
+        off += 4
+        name = raw[off:off + nlen].decode()
+        off += nlen
+        (ndim,) = struct.unpack_from("<I", raw, off)
+        off += 4
+        dims = struct.unpack_from(f"<{ndim}Q", raw, off)
+        off += 8 * ndim
+        n = int(np.prod(dims)) if ndim else 1
+        out[name] = np.frombuffer(raw, dtype="<f4", count=n, offset=off).reshape(dims).copy()
+        off += 4 * n
+    return out
+
+
+def sha(x: np.ndarray) -> str:
+    return hashlib.sha256(np.ascontiguousarray(x, dtype="<f4").tobytes()).hexdigest()
+
+
+# The seeded configurations the parity tests use, built exactly like a program using the
+# reference would build them: manual_seed, then tensors drawn in this order.
+def config_inputs(name: str, rng_factory):
+    if name == "cfg1_512":  # bench_matmul-shaped product, U[-1,1], seed 0
+        g = rng_factory(0)
+        return g.rand((512, 512), -1.0, 1.0), g.rand((512, 512), -1.0, 1.0)
+    if name == "det_200x150x120":  # tests/test_tensor.cpp:456-476
+        g = rng_factory(7)
+        return g.randn((200, 150)), g.randn((150, 120))
+    if name == "cfg4_relu_256":  # half-zero A, reduced size of the relu-sparse case, seed 4
+        g = rng_factory(4)
+        a = np.maximum(g.randn((256, 256)), 0.0).astype(np.float32)
+        return a, g.randn((256, 256))
+    if name == "cfg2_scores":  # batched per-head Q x K^T operands (K^T materialised), seed 2
+        g = rng_factory(2)
+        q = g.randn((8, 64, 24))
+        k = g.randn((8, 64, 24))
+        return q, np.ascontiguousarray(np.swapaxes(k, 1, 2))
+    if name == "cfg2_shared":  # (B, M, K) x (K, N): Linear on a batch, Xavier-uniform weight
+        g = rng_factory(2)
+        x = g.randn((4, 64, 96))
+        bound = float(np.sqrt(6.0 / (96 + 121)))
+        return x, g.rand((96, 121), -bound, bound)
+    raise KeyError(name)
+
+
+CONFIGS = ["cfg1_512", "det_200x150x120", "cfg4_relu_256", "cfg2_scores", "cfg2_shared"]
+
+
+class RefRng:
+    """The reference engine's own global generator."""
+
+    def __init__(self, seed: int):
+        import ctypes
+
+        orc.ref().ref_manual_seed(ctypes.c_uint64(seed))
+
+    def rand(self, shape, lo=-1.0, hi=1.0):
+        import ctypes
+
+        out = np.empty(shape, dtype=np.float32)
+        orc.ref().ref_rand(out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), ctypes.c_size_t(out.size),
+                           ctypes.c_float(lo), ctypes.c_float(hi))
+        return out
+
+    def randn(self, shape, mean=0.0, stddev=1.0):
+        import ctypes
+
+        out = np.empty(shape, dtype=np.float32)
+        orc.ref().ref_randn(out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), ctypes.c_size_t(out.size),
+                            ctypes.c_float(mean), ctypes.c_float(stddev))
+        return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ref_dir = Path(args.reference)
+
+    # 1. the reference's PyTorch golden vectors
+    packed = {}
+    for name in ["matmul", "matmul_batched", "matmul_shared"]:
+        fx = read_fixture(ref_dir / "tests" / "fixtures" / f"{name}.bin")
+        for key, val in fx.items():
+            packed[f"{name}/{key}"] = val
+    np.savez(HERE / "pytorch_matmul.npz", **packed)
+
+    # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
+    known = [
+        {"a_shape": [2, 3], "a": [1, 2, 3, 4, 5, 6], "b_shape": [3, 2], "b": [7, 8, 9, 1, 2, 3],
+         "out_shape": [2, 2], "out": [31, 19, 85, 55]},
+        {"a_shape": [2, 2, 3], "a": list(range(1, 13)), "b_shape": [2, 3, 2],
+         "b": [1, 0, 0, 1, 1, 1, 2, 0, 0, 2, 1, 1], "out_shape": [2, 2, 2],
+         "out_at": {"0": 4, "1": 5, "4": 23}},
+        {"a_shape": [2, 2, 3], "a": list(range(1, 13)), "b_shape": [3, 2], "b": [1, 0, 0, 1, 1, 1],
+         "out_shape": [2, 2, 2], "out_at": {"0": 4, "4": 16}},
+    ]
+    throws = [
+        {"a_shape": [2, 3], "b_shape": [2, 3], "why": "incompatible inner dimensions"},
+        {"a_shape": [2, 2, 3], "b_shape": [3, 3, 2], "why": "mismatched batches"},
+        {"a_shape": [4], "b_shape": [4], "why": "1-D operands"},
+    ]
+    (HERE / "known_answers.json").write_text(json.dumps({"products": known, "throws": throws}, indent=1))
+
+    # 3. outputs of the unmodified reference engine
+    runs = {}
+    for seed in (0, 1, 7):
+        g = RefRng(seed)
+        runs[f"rng/seed{seed}/rand"] = g.rand((33,), -1.0, 1.0)
+        runs[f"rng/seed{seed}/randn"] = g.randn((33,), 0.5, 2.0)
+        runs[f"rng/seed{seed}/rand_after"] = g.rand((4,), 0.0, 1.0)
+    meta = {}
+    for name in CONFIGS:
+        a, b = config_inputs(name, RefRng)
+        c = orc.ref_matmul(a, b)
+        flat = c.reshape(-1)
+        step = max(1, flat.size // 509)
+        runs[f"{name}/sample"] = flat[::step].copy()
+        meta[name] = {"a_sha256": sha(a), "b_sha256": sha(b), "out_sha256": sha(c), "sample_step": step,
+                      "out_shape": list(c.shape)}
+        # gradients through the reference's autograd for an explicit grad_output
+        import ctypes
+
+        gseed = RefRng(99)
+        gout = gseed.randn(c.shape)
+        ga, gb = np.empty_like(a), np.empty_like(b)
+        fp = ctypes.POINTER(ctypes.c_float)
+        dims = c.shape[:-2]
+        batch = int(np.prod(dims)) if dims else 1
+        rc = orc.ref().ref_matmul_backward(
+            a.ctypes.data_as(fp), b.ctypes.data_as(fp), gout.ctypes.data_as(fp), None,
+            ga.ctypes.data_as(fp), gb.ctypes.data_as(fp), ctypes.c_size_t(batch),
+            ctypes.c_size_t(a.shape[-2]), ctypes.c_size_t(a.shape[-1]), ctypes.c_size_t(b.shape[-1]),
+            int(a.ndim > 2), int(b.ndim > 2))
+        assert rc == 0
+        meta[name]["grad_a_sha256"] = sha(ga)
+        meta[name]["grad_b_sha256"] = sha(gb)
+    np.savez(HERE / "reference_runs.npz", **runs)
+    (HERE / "reference_runs.json").write_text(json.dumps(meta, indent=1))
+    print("wrote", [p.name for p in sorted(HERE.glob("*.np*"))], "known_answers.json reference_runs.json")
+
+
+if __name__ == "__main__":
+    main()
