@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the fp32-accurate GEMM hot path.
+
+    python bench.py --gpus 1 --steps K --warmup W            this library, one B200
+    torchrun ... bench.py --gpus N --steps K --warmup W      N-column-sharded over N GPUs
+    python bench.py --impl reference ...                     the reference's own CPU matmul
+
+A step is one product C = A x B of the large-square configuration: 16384^3 fp32, A and B
+i.i.d. N(0, 1/K) (seeded, generated on the device: synthetic), B and C split by column blocks
+over the ranks, every rank ending with all of C.  Total work is fixed as N grows (strong
+scaling).  At N = 1 the 4096^3 product of the headline metric is measured too and reported
+under "gemm_4096".
+
+One JSON line is printed by rank 0.  `value` is useful TFLOP/s = 2*M*N*K / time (the three
+TF32 products per term and the split are overhead, not counted).  `roofline.achieved` counts
+the tensor-core math actually issued (3 x useful in the default 3xTF32 mode) against the TF32
+tensor-pipe rate measured in the same run with cuBLAS.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fp32-accurate GEMM TFLOP/s at 4096^3 (1 GPU) and 16384^3 (1/2/4/8 B200), % roofline"
+BIG = 16384
+SMALL = 4096
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--size", type=int, default=BIG, help="square size of the main workload")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
+    ap.add_argument("--no-extras", action="store_true", help="skip 4096^3, e2e and the CPU baseline")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples taken while the GPU was actually loaded: the upper half by power draw
+        if sm:
+            cut = statistics.median(power) if power else 0
+            loaded = [c for c, p in zip(sm, power) if p >= cut] or sm
+            return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                    "samples": len(sm), "power_w_max": max(power) if power else None}
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU reference arm
+# ------------------------------------------------------------------------------------------
+def cpu_sample(n: int, rows: int, repeats: int = 1):
+    """Times the reference's CPU matmul on `rows` rows of the n^3 product (rows are independent
+    in its loop, so this is an exact slice of the full job).  Returns (TFLOP/s, info)."""
+    import numpy as np
+
+    from oracle import oracle_py as orc
+
+    rng = np.random.default_rng(1)
+    scale = 1.0 / np.sqrt(n)
+    a = (rng.standard_normal((rows, n), dtype=np.float32) * scale).astype(np.float32)
+    b = (rng.standard_normal((n, n), dtype=np.float32) * scale).astype(np.float32)
+    if orc.have_ref():
+        kind, cores = "reference", orc.ref_threads()
+        secs = orc.ref_matmul_time(a, b, repeats)
+    else:
+        kind, cores = "port", os.cpu_count() or 1
+        best = float("inf")
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            orc.matmul(a, b)
+            best = min(best, time.perf_counter() - t0)
+        secs = best
+    flops = 2.0 * rows * n * n
+    return flops / secs / 1e12, {"kind": kind, "cores": cores, "seconds": secs,
+                                 "sample": f"{rows} of {n} output rows of the {n}^3 product "
+                                           f"(best of {repeats}), all host threads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = args.size
+    rows = 64 if n >= 8192 else 256
+    tf, info = cpu_sample(n, rows, 1)  # warm-up, also sizes the job
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_sample(n, rows, 1)
+    vals = []
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, info = cpu_sample(n, rows, 1)
+        vals.append(v)
+        if time.perf_counter() - t0 > 150:
+            break
+    value = statistics.mean(vals)
+    ms = 2.0 * rows * n * n / (value * 1e12) * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": len(vals), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"fp32 GEMM {n}^3, N(0,1/K) inputs; CPU arm times a row slice per step",
+                   "M": n, "N": n, "K": n},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
+                         "sample": info["sample"]},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def measure_tf32_peak(torch, dev, seconds: float = 1.5):
+    """cuBLAS TF32 8192^3: best single launch (burst) and the rate of a back-to-back loop
+    (sustained, what a kernel timed inside a long step should be held against)."""
+    n = 8192
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn((n, n), device=dev)
+        b = torch.randn((n, n), device=dev)
+        c = torch.empty((n, n), device=dev)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(10):
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        burst = 2.0 * n ** 3 / best / 1e9
+        iters = max(10, int(seconds * 1e3 / best))
+        e0.record()
+        for _ in range(iters):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        sustained = 2.0 * n ** 3 * iters / e0.elapsed_time(e1) / 1e9
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    del a, b, c
+    return burst, sustained
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    pkg.load()  # raises if the CUDA library is missing: there is no fallback
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    precision = pkg.PRECISION_3XTF32 if args.precision == "3xtf32" else pkg.PRECISION_TF32
+    kfac = 3 if args.precision == "3xtf32" else 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n = args.size
+    gen = torch.Generator(device=dev).manual_seed(1)  # same bytes on every rank
+    A = torch.randn((n, n), device=dev, generator=gen) / n ** 0.5
+    B = torch.randn((n, n), device=dev, generator=gen) / n ** 0.5
+    exchange = args.exchange if world > 1 else "none"
+    try:
+        op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev,
+                                           mode=args.exchange if world > 1 else "nccl")
+    except Exception as exc:  # symmetric memory unavailable: the NCCL gather still works
+        if world > 1 and args.exchange == "fused":
+            if rank == 0:
+                print(f"[bench] fused exchange unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
+            exchange = "nccl"
+            op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev, mode="nccl")
+        else:
+            raise
+    if precision != pkg.PRECISION_3XTF32:
+        def block(A_, B_, dests, col0, cols, _op=op):
+            pkg.gemm_colshard(A_, B_, dests, M=n, N=n, K=n, col0=col0, cols=cols, lda=n, ldb=n, ldc=n,
+                              precision=precision)
+        op._compute = block
+
+    def step():
+        op(A, B)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    pkg.status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = pkg.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    total_ms = max_over_ranks(e0.elapsed_time(e1))
+    launches = pkg.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    pkg.status()
+    ms = total_ms / args.steps
+    flops = 2.0 * n ** 3
+    value = flops / ms / 1e9
+
+    # parity spot check of the timed result: sampled rows against fp64 on the device
+    rows = torch.arange(3, n, max(1, n // 16), device=dev)
+    ref = A[rows].double() @ B.double()
+    err = float(((op.C[rows].double() - ref).abs() / ref.abs().clamp(min=1.0)).max().item())
+    del ref
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)"
+            if kfac == 3 else "tf32", "data": "synthetic",
+            "config": {"workload": f"fp32 GEMM {n}^3, A,B ~ N(0,1/K) seed 1, C N-column-sharded over "
+                                   f"{world} GPU(s), every rank ends with all of C",
+                       "M": n, "N": n, "K": n, "exchange": exchange, "precision": args.precision,
+                       "l2": "operands (1 GiB each) far exceed L2; no flush needed"
+                       if n >= 8192 else "L2 flushed between timed launches"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "check": {"scaled_max_error_vs_fp64_sampled_rows": err},
+        }
+
+    extras = (world == 1 and not args.no_extras)
+    # ------------------------------------------------------------------ roofline (rank 0, N = 1)
+    if rank == 0 and world == 1:
+        burst, sustained = measure_tf32_peak(torch, dev)
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        bf16 = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+        achieved = kfac * value
+        line["roofline"] = {
+            "bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s",
+            "frac": achieved / sustained, "traffic": None,
+            "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per launch "
+                    f"(2*M*N*K*{kfac}) / mean launch time by CUDA events; peak = cuBLAS TF32 8192^3 "
+                    f"sustained loop measured in this run (of measured); burst {burst:.1f}",
+            "useful_tflops": value, "useful_frac": value / sustained, "k_factor": kfac,
+            "peak_burst": burst,
+            "bf16_measured_peaks": {k: bf16.get(k) for k in ("bf16_tflops", "bf16_tflops_sustained")},
+        }
+    if world > 1 and rank == 0:
+        line["roofline"] = {"bound": "tensor", "achieved": kfac * value, "peak": None, "unit": "TFLOP/s",
+                            "frac": None, "traffic": None,
+                            "note": "whole-job tensor math over all ranks; see the N=1 line for the per-GPU peak"}
+
+    # ------------------------------------------------------------------ 4096^3 (N = 1)
+    if extras:
+        m = SMALL
+        a4 = torch.randn((m, m), device=dev, generator=gen) / m ** 0.5
+        b4 = torch.randn((m, m), device=dev, generator=gen) / m ** 0.5
+        c4 = torch.empty((m, m), device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            pkg.gemm(a4, b4, c4, batch=1, M=m, N=m, K=m, lda=m, ldb=m, ldc=m, precision=precision)
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(max(20, args.steps)):
+            flush.fill_(1)  # evict A, B, C from L2 between timed launches
+            e0.record()
+            pkg.gemm(a4, b4, c4, batch=1, M=m, N=m, K=m, lda=m, ldb=m, ldc=m, precision=precision)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        pkg.status()
+        mean_ms = statistics.mean(times)
+        tf = 2.0 * m ** 3 / mean_ms / 1e9
+        line["gemm_4096"] = {
+            "workload": "fp32 GEMM 4096^3, N(0,1/K), one launch per timing, L2 flushed between launches",
+            "ms_mean": mean_ms, "ms_best": min(times), "useful_tflops": tf,
+            "tensor_math_tflops": kfac * tf, "frac_of_tf32_peak": kfac * tf / line["roofline"]["peak_burst"],
+            "peak": line["roofline"]["peak_burst"], "peak_kind": "cuBLAS TF32 burst (kernel timed alone)",
+        }
+        del a4, b4, c4, flush
+
+    # ------------------------------------------------------------------ end to end, host buffers
+    if world == 1 and not args.no_extras:
+        import numpy as np
+
+        h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+        h_b = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+        h_c = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+        h_a.copy_(A)
+        h_b.copy_(B)
+        del op
+        torch.cuda.empty_cache()
+        na, nb, nc = h_a.numpy(), h_b.numpy(), h_c.numpy()
+        reps = max(2, min(args.steps, 4))
+        pkg.matmul_host(na, nb, nc, batch=1, rows=n, inner=n, cols=n, a_batched=False, b_batched=False)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            pkg.matmul_host(na, nb, nc, batch=1, rows=n, inner=n, cols=n, a_batched=False, b_batched=False)
+        secs = (time.perf_counter() - t0) / reps
+        line["e2e"] = {"value": flops / secs / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(2 * n * n * 4),
+                       "d2h_bytes_per_step": int(n * n * 4), "ms_per_step": secs * 1e3,
+                       "path": "b200_matmul_f32_host: pinned host A,B -> device, kernel, C -> pinned host, synchronised"}
+        assert np.isfinite(nc[::997, ::991]).all()
+    elif world > 1:
+        # every rank uploads A and its B columns from pinned memory and downloads its C columns
+        col0, cols = op.col0, op.cols
+        h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+        h_b = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)
+        h_c = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)
+        h_a.copy_(A)
+        if cols:
+            h_b.copy_(B[:, col0:col0 + cols])
+        reps = max(2, min(args.steps, 4))
+
+        def e2e_step():
+            A.copy_(h_a, non_blocking=True)
+            if cols:
+                B[:, col0:col0 + cols].copy_(h_b, non_blocking=True)
+            op(A, B)
+            if cols:
+                h_c.copy_(op.C[:, col0:col0 + cols], non_blocking=True)
+            torch.cuda.synchronize()
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            e2e_step()
+        barrier()
+        secs = max_over_ranks((time.perf_counter() - t0) / reps * 1e3) / 1e3
+        if rank == 0:
+            line["e2e"] = {"value": flops / secs / 1e12, "unit": "TFLOP/s",
+                           "h2d_bytes_per_step": int((n * n + n * cols) * 4), "d2h_bytes_per_step": int(n * cols * 4),
+                           "ms_per_step": secs * 1e3,
+                           "path": "per rank: pinned host A + B columns -> device, sharded kernel + exchange, "
+                                   "own C columns -> pinned host; bytes are per rank"}
+    elif rank == 0:
+        line["e2e"] = None
+
+    # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1)
+    if rank == 0 and world == 1 and not args.no_extras:
+        tf, info = cpu_sample(n, 64, 1)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
+                                "sample": info["sample"]}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
