@@ -72,6 +72,9 @@ struct GemmParams {
     uint32_t idesc;
     // loader / epilogue fast paths
     int a_vec_ok, b_vec_ok, c_vec_ok;
+#ifdef B200_PHASE_PROFILE
+    unsigned long long* prof;  // development only: cycles per phase, CTA 0
+#endif
 };
 
 template <int BN, int BK>
@@ -131,6 +134,22 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
         }
     }
 }
+
+#ifdef B200_PHASE_PROFILE
+#define B200_T0() const long long _t0 = clock64()
+#define B200_T1(idx) _prof[idx] += clock64() - _t0
+#define B200_PROF_DECL long long _prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define B200_PROF_FLUSH(cond)                                                        \
+    if ((cond) && blockIdx.x == 0 && p.prof) {                                       \
+        for (int _i = 0; _i < 12; ++_i)                                              \
+            if (_prof[_i]) atomicAdd(p.prof + _i, (unsigned long long)_prof[_i]);    \
+    }
+#else
+#define B200_T0()
+#define B200_T1(idx)
+#define B200_PROF_DECL
+#define B200_PROF_FLUSH(cond)
+#endif
 
 // Loads a ROWS x 32 tile of one operand with plain global loads, splits it and stores the
 // head / tail tiles in the K-major 128-byte-swizzled layout.  `k_contig`: k is the contiguous
@@ -266,6 +285,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         if (kTma && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            B200_PROF_DECL;
             for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
                 const Work wk = decode_work(p, w);
                 const int za = p.strideA ? wk.b : 0;
@@ -273,10 +293,15 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 for (int kb = wk.kb0; kb < wk.kb1; ++kb, ++it) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
-                    if (!wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
-                                  kStatProducer)) {
-                        ok = false;
-                        break;
+                    {
+                        B200_T0();
+                        const bool got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag,
+                                                  p.status, kStatProducer);
+                        B200_T1(0);
+                        if (!got) {
+                            ok = false;
+                            break;
+                        }
                     }
                     const uint32_t full = smem_u32(&full_bar[s]);
                     const uint32_t sa = smem_u32(smem) + s * Cfg::kStageBytes;
@@ -300,6 +325,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
+            B200_PROF_FLUSH(true);
             if (!ok) {
                 // Leave no bulk copy in flight behind an exiting CTA: give the loads already
                 // issued a short while to land.
@@ -320,6 +346,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             const uint32_t idesc = p.idesc;
             uint32_t it = 0, chain = 0;
             bool ok = true;
+            B200_PROF_DECL;
             for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
                 const Work wk = decode_work(p, w);
                 const int nkb = wk.kb1 - wk.kb0;
@@ -330,15 +357,24 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const bool chain_end = ((i + 1) % promote_every) == 0 || i == nkb - 1;
                     const uint32_t buf = chain & 1;
                     if (chain_start) {
-                        if (!wait_bar(smem_u32(&acce_bar[buf]), ((chain >> 1) & 1) ^ 1, abort_flag,
-                                      p.status, kStatMma)) {
+                        B200_T0();
+                        const bool got = wait_bar(smem_u32(&acce_bar[buf]), ((chain >> 1) & 1) ^ 1,
+                                                  abort_flag, p.status, kStatMma);
+                        B200_T1(2);
+                        if (!got) {
                             ok = false;
                             break;
                         }
                     }
-                    if (!wait_bar(smem_u32(&split_bar[s]), ph, abort_flag, p.status, kStatMma)) {
-                        ok = false;
-                        break;
+                    {
+                        B200_T0();
+                        const bool got =
+                            wait_bar(smem_u32(&split_bar[s]), ph, abort_flag, p.status, kStatMma);
+                        B200_T1(3);
+                        if (!got) {
+                            ok = false;
+                            break;
+                        }
                     }
                     tc_fence_after_sync();
                     const uint32_t d = tmem + buf * BN;
@@ -372,6 +408,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
+            B200_PROF_FLUSH(true);
         }
       }
     } else {
@@ -384,14 +421,21 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         float acc[kCols];
         uint32_t it = 0, chain = 0;
         bool ok = true;
+        B200_PROF_DECL;
 
         // Adds the finished TMEM partial of accumulator chain `c` into the fp32 registers.
         auto promote = [&](uint32_t c) -> bool {
             const uint32_t buf = c & 1;
-            bool got = wait_bar(smem_u32(&accf_bar[buf]), (c >> 1) & 1, abort_flag, p.status,
-                                kStatWorkerAcc);
-            got = __all_sync(0xffffffffu, got);
+            bool got;
+            {
+                B200_T0();
+                got = wait_bar(smem_u32(&accf_bar[buf]), (c >> 1) & 1, abort_flag, p.status,
+                               kStatWorkerAcc);
+                got = __all_sync(0xffffffffu, got);
+                B200_T1(7);
+            }
             if (!got) return false;
+            B200_T0();
             tc_fence_after_sync();
             const uint32_t t0 = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN +
                                 half * kCols;
@@ -414,6 +458,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acce_bar[buf]));
+            B200_T1(8);
             return true;
         };
 
@@ -428,13 +473,19 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const uint32_t ph = (it / kStages) & 1;
                 uint8_t* stage = smem + s * Cfg::kStageBytes;
                 if constexpr (kTma) {
-                    bool got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status,
-                                        kStatWorkerFull);
-                    got = __all_sync(0xffffffffu, got);
+                    bool got;
+                    {
+                        B200_T0();
+                        got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                                       kStatWorkerFull);
+                        got = __all_sync(0xffffffffu, got);
+                        B200_T1(5);
+                    }
                     if (!got) {
                         ok = false;
                         break;
                     }
+                    B200_T0();
                     float4* hi = reinterpret_cast<float4*>(stage);
                     float4* lo = reinterpret_cast<float4*>(stage + Cfg::kHalf);
                     constexpr int kN4 = Cfg::kHalf / 16;
@@ -449,6 +500,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         hi[q] = h;
                         if (prec3) lo[q] = l;
                     }
+                    B200_T1(6);
                 } else {
                     bool got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
                                         kStatWorkerFull);
@@ -543,6 +595,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 }
             }
         }
+        B200_PROF_FLUSH(wtid == 0);
     }
 
     tc_fence_before_sync();

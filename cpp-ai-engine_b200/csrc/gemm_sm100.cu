@@ -39,6 +39,9 @@ struct Options {
     long k_block = 32;
 };
 Options g_opt;
+#ifdef B200_PHASE_PROFILE
+unsigned long long* g_prof = nullptr;  // development builds only
+#endif
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -319,6 +322,9 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     p.promote_every = g_opt.promote_every >= 1 ? static_cast<int>(g_opt.promote_every) : 1;
     p.partial = static_cast<float*>(workspace);
     p.status = st.status;
+#ifdef B200_PHASE_PROFILE
+    p.prof = g_prof;
+#endif
     p.a_vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (lda & 3) == 0 &&
                   (strideA & 3) == 0)
                      ? 1
@@ -392,6 +398,11 @@ int grow(void** ptr, size_t* cap, size_t need) {
 using namespace b200;
 
 extern "C" {
+
+#ifdef B200_PHASE_PROFILE
+// Development builds only: device array of 12 cycle counters filled by CTA 0.
+void b200_dev_set_profile_buffer(unsigned long long* buf) { g_prof = buf; }
+#endif
 
 int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
                   int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,

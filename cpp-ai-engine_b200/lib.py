@@ -7,6 +7,7 @@ to the library and raises :class:`B200Error` on a non-zero return.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 from typing import Optional, Sequence
 
@@ -46,10 +47,11 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB.exists():
+    path = Path(os.environ.get("B200_GEMM_LIBRARY", str(LIB)))  # override: an alternative build
+    if not path.exists():
         raise RuntimeError(
-            f"{LIB} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()')")
-    lib = ctypes.CDLL(str(LIB))
+            f"{path} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()')")
+    lib = ctypes.CDLL(str(path))
     c_i64, c_f, c_vp, c_sz, c_int = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     lib.b200_gemm_f32.restype = c_int
     lib.b200_gemm_f32.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
