@@ -30,6 +30,13 @@
 // global loads, split in registers and store straight into the K-major swizzled layout; the
 // TMA warp idles.  Same MMA and epilogue code.
 //
+// Pair mode (kPair): two CTAs of a cluster form one 256 x BN tile.  Each CTA loads and splits
+// 128 rows of A and HALF of the tile's B columns, and the leader CTA's MMA lane issues
+// cta_group::2 products that read both CTAs' shared memory and write 128 accumulator rows
+// into each CTA's TMEM.  Per CTA that cuts the shared-memory traffic of a k-block (raw tile
+// in, head/tail out, operand fetches) by a third and the stage to 64 KB, so three stages fit.
+// No TMA load is multicast: every CTA fetches only what it alone needs.
+//
 // Every wait is bounded (see sm100_ptx.cuh).  A wait that runs out records a bit in
 // *status, raises a CTA-wide abort flag that all other waits poll, and every role falls
 // through to the common exit where TMEM is released.
@@ -77,12 +84,13 @@ struct GemmParams {
 #endif
 };
 
-template <int BN, int BK>
+template <int BN, int BK, bool kPair = false>
 struct TileCfg {
     static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
     static_assert(BK == 16 || BK == 32, "unsupported k-block");
     static constexpr uint32_t kABytes = kBM * BK * 4;
-    static constexpr uint32_t kBBytes = BN * BK * 4;
+    static constexpr int kBCols = kPair ? BN / 2 : BN;  // B columns held by one CTA
+    static constexpr uint32_t kBBytes = kBCols * BK * 4;
     static constexpr uint32_t kHalf = kABytes + kBBytes;  // raw / head tiles; tails follow
     static constexpr uint32_t kStageBytes = 2 * kHalf;
     static constexpr int kMaxStages = (227 * 1024 - 2048) / kStageBytes;
@@ -117,14 +125,17 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int w) {
     return r;
 }
 
+// kCluster: the barrier is also arrived on by the peer CTA, whose writes must be acquired.
+template <bool kCluster = false>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                          int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto probe = [&]() { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (probe()) return true;
     const uint64_t start = global_timer_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
+            if (probe()) return true;
         }
         if (*abort_flag) return false;
         if (global_timer_ns() - start > kWaitBudgetNs) {
@@ -222,14 +233,17 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
     }
 }
 
-template <int BN, int BK, bool kTma>
+template <int BN, int BK, bool kTma, bool kPair = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                  const __grid_constant__ CUtensorMap mapB) {
-    using Cfg = TileCfg<BN, BK>;
+    using Cfg = TileCfg<BN, BK, kPair>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kCols = Cfg::kCols;
+    constexpr int kTileM = kPair ? 2 * kBM : kBM;        // rows of C per tile
+    constexpr int kArrivals = kPair ? 2 * kWorkerWarps : kWorkerWarps;
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
+    static_assert(!kPair || kTma, "pair mode loads with TMA");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -246,31 +260,45 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     volatile int* abort_flag = &abort_s;
+    // In pair mode the two CTAs of a cluster walk the same tiles; CTA 0 is the leader.
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+    const int first_work = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int work_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
-            mbar_init(smem_u32(&split_bar[s]), kWorkerWarps);
+            mbar_init(smem_u32(&split_bar[s]), kArrivals);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&accf_bar[b]), 1);
-            mbar_init(smem_u32(&acce_bar[b]), kWorkerWarps);
+            mbar_init(smem_u32(&acce_bar[b]), kArrivals);
         }
         abort_s = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
         __syncwarp();
-        tmem_alloc(smem_u32(&tmem_base_s), Cfg::kTmemCols);
-        tmem_relinquish();
+        if constexpr (kPair) {
+            tmem_alloc_pair(smem_u32(&tmem_base_s), Cfg::kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(&tmem_base_s), Cfg::kTmemCols);
+            tmem_relinquish();
+        }
     }
     if (kTma && warp == 0 && lane == 0) {
         tma_prefetch_desc(&mapA);
         tma_prefetch_desc(&mapB);
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (kPair) {
+        __syncwarp();
+        cluster_sync();  // both CTAs' barriers exist before either signals the other
+    } else {
+        __syncthreads();
+    }
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
     const bool prec3 = (p.precision == 0);
@@ -286,7 +314,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             uint32_t it = 0;
             bool ok = true;
             B200_PROF_DECL;
-            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+            for (int w = first_work; w < p.total_work && ok; w += work_stride) {
                 const Work wk = decode_work(p, w);
                 const int za = p.strideA ? wk.b : 0;
                 const int zb = p.strideB ? wk.b : 0;
@@ -307,21 +335,21 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const uint32_t sa = smem_u32(smem) + s * Cfg::kStageBytes;
                     const uint32_t sb = sa + Cfg::kABytes;
                     mbar_arrive_expect_tx(full, Cfg::kHalf);
+                    const int row0 = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM;
+                    const int col0 = wk.nt * BN + static_cast<int>(cta_rank) * Cfg::kBCols;
                     if (!p.transA) {
-                        tma_load_3d(sa, &mapA, full, kb * BK, wk.mt * kBM, za);
+                        tma_load_3d(sa, &mapA, full, kb * BK, row0, za);
                     } else {
 #pragma unroll
                         for (int j = 0; j < kBM / 32; ++j)
-                            tma_load_3d(sa + j * (BK * 128), &mapA, full, wk.mt * kBM + j * 32,
-                                        kb * BK, za);
+                            tma_load_3d(sa + j * (BK * 128), &mapA, full, row0 + j * 32, kb * BK, za);
                     }
                     if (p.transB) {
-                        tma_load_3d(sb, &mapB, full, kb * BK, wk.nt * BN, zb);
+                        tma_load_3d(sb, &mapB, full, kb * BK, col0, zb);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 32; ++j)
-                            tma_load_3d(sb + j * (BK * 128), &mapB, full, wk.nt * BN + j * 32,
-                                        kb * BK, zb);
+                        for (int j = 0; j < Cfg::kBCols / 32; ++j)
+                            tma_load_3d(sb + j * (BK * 128), &mapB, full, col0 + j * 32, kb * BK, zb);
                     }
                 }
             }
@@ -337,17 +365,33 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         }
       } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && cta_rank == 0) {
             const uint32_t s0 = smem_u32(smem);
             const uint64_t dA_hi = make_smem_desc(s0, p.a_lbo, p.a_sbo, p.a_layout);
             const uint64_t dB_hi = make_smem_desc(s0 + Cfg::kABytes, p.b_lbo, p.b_sbo, p.b_layout);
             const uint32_t ka = p.a_kstep >> 4, kb_step = p.b_kstep >> 4;
             constexpr uint32_t kLoOff = Cfg::kHalf >> 4;
             const uint32_t idesc = p.idesc;
+            auto issue_mma = [](uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t accum) {
+                if constexpr (kPair) {
+                    mma_tf32_ss_pair(d, a, b, id, accum);
+                } else {
+                    mma_tf32_ss(d, a, b, id, accum);
+                }
+            };
+            // completion of everything issued so far -> the barrier at this offset in the CTA
+            // (in both CTAs of a pair)
+            auto signal_done = [](uint32_t bar) {
+                if constexpr (kPair) {
+                    tc_commit_pair(bar, 3);
+                } else {
+                    tc_commit(bar);
+                }
+            };
             uint32_t it = 0, chain = 0;
             bool ok = true;
             B200_PROF_DECL;
-            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+            for (int w = first_work; w < p.total_work && ok; w += work_stride) {
                 const Work wk = decode_work(p, w);
                 const int nkb = wk.kb1 - wk.kb0;
                 for (int i = 0; i < nkb; ++i, ++it) {
@@ -358,8 +402,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const uint32_t buf = chain & 1;
                     if (chain_start) {
                         B200_T0();
-                        const bool got = wait_bar(smem_u32(&acce_bar[buf]), ((chain >> 1) & 1) ^ 1,
-                                                  abort_flag, p.status, kStatMma);
+                        const bool got = wait_bar<kPair>(smem_u32(&acce_bar[buf]),
+                                                         ((chain >> 1) & 1) ^ 1, abort_flag,
+                                                         p.status, kStatMma);
                         B200_T1(2);
                         if (!got) {
                             ok = false;
@@ -368,8 +413,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                     {
                         B200_T0();
-                        const bool got =
-                            wait_bar(smem_u32(&split_bar[s]), ph, abort_flag, p.status, kStatMma);
+                        const bool got = wait_bar<kPair>(smem_u32(&split_bar[s]), ph, abort_flag,
+                                                         p.status, kStatMma);
                         B200_T1(3);
                         if (!got) {
                             ok = false;
@@ -389,8 +434,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         for (int ks = 0; ks < BK / 8; ++ks) {
                             const uint64_t ah = dA_hi + (soff + ks * ka);
                             const uint64_t bh = dB_hi + (soff + ks * kb_step);
-                            mma_tf32_ss(d, ah + kLoOff, bh, idesc, accumulate);
-                            mma_tf32_ss(d, ah, bh + kLoOff, idesc, 1u);
+                            issue_mma(d, ah + kLoOff, bh, idesc, accumulate);
+                            issue_mma(d, ah, bh + kLoOff, idesc, 1u);
                             accumulate = 1u;
                         }
                     }
@@ -398,12 +443,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     for (int ks = 0; ks < BK / 8; ++ks) {
                         const uint64_t ah = dA_hi + (soff + ks * ka);
                         const uint64_t bh = dB_hi + (soff + ks * kb_step);
-                        mma_tf32_ss(d, ah, bh, idesc, accumulate);
+                        issue_mma(d, ah, bh, idesc, accumulate);
                         accumulate = 1u;
                     }
-                    tc_commit(smem_u32(&empty_bar[s]));
+                    signal_done(smem_u32(&empty_bar[s]));
                     if (chain_end) {
-                        tc_commit(smem_u32(&accf_bar[buf]));
+                        signal_done(smem_u32(&accf_bar[buf]));
                         ++chain;
                     }
                 }
@@ -422,6 +467,15 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         uint32_t it = 0, chain = 0;
         bool ok = true;
         B200_PROF_DECL;
+
+        // split_bar / acce_bar are waited on by the MMA lane of the leader CTA only.
+        auto arrive_at_leader = [&](uint32_t bar) {
+            if constexpr (kPair) {
+                mbar_arrive_cluster(map_to_cta(bar, 0));
+            } else {
+                mbar_arrive(bar);
+            }
+        };
 
         // Adds the finished TMEM partial of accumulator chain `c` into the fp32 registers.
         auto promote = [&](uint32_t c) -> bool {
@@ -457,12 +511,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&acce_bar[buf]));
+            if (lane == 0) arrive_at_leader(smem_u32(&acce_bar[buf]));
             B200_T1(8);
             return true;
         };
 
-        for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+        for (int w = first_work; w < p.total_work && ok; w += work_stride) {
             const Work wk = decode_work(p, w);
             const int nkb = wk.kb1 - wk.kb0;
 #pragma unroll
@@ -521,7 +575,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 // generic-proxy writes -> visible to the tensor core's async-proxy reads
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&split_bar[s]));
+                if (lane == 0) arrive_at_leader(smem_u32(&split_bar[s]));
 
                 // Drain the chain that ended one k-block ago (its MMAs have had a whole
                 // k-block of time to finish, so this rarely waits).
@@ -541,7 +595,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             ++chain;
 
             // ---------------------------------------------------------------- epilogue
-            const int row = wk.mt * kBM + quarter * 32 + lane;
+            const int row = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
             const int col0 = wk.nt * BN + half * kCols;
             if (row < p.M && col0 < p.N) {
                 if (p.split_k > 1) {
@@ -599,10 +653,21 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     }
 
     tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) {
+    if constexpr (kPair) {
+        // Neither CTA may release TMEM or exit while the other can still be the target of a
+        // pair product, a completion signal or a remote arrive.
         __syncwarp();
-        tmem_dealloc(tmem, Cfg::kTmemCols);
+        cluster_sync();
+        if (warp == 1) {
+            __syncwarp();
+            tmem_dealloc_pair(tmem, Cfg::kTmemCols);
+        }
+    } else {
+        __syncthreads();
+        if (warp == 1) {
+            __syncwarp();
+            tmem_dealloc(tmem, Cfg::kTmemCols);
+        }
     }
 }
 

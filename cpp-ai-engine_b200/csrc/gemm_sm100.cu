@@ -37,6 +37,7 @@ struct Options {
     long promote_every = 1;
     long force_ldg = 0;
     long k_block = 32;
+    long pair_mode = 0;  // 0 automatic, 1 never, 2 whenever legal
 };
 Options g_opt;
 #ifdef B200_PHASE_PROFILE
@@ -171,6 +172,57 @@ int launch_cfg(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mb
     return static_cast<int>(cudaGetLastError());
 }
 
+// CTA-pair kernel (tile 256 x 256): launched as clusters of two CTAs.
+int max_pair_clusters(int dev) {
+    static int cached[kMaxDevices] = {};
+    if (cached[dev] > 0) return cached[dev];
+    using Cfg = TileCfg<256, 32, true>;
+    auto kernel = gemm_tf32_kernel<256, 32, true, true>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(Cfg::kSmemBytes)) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cached[dev] = n;
+    return n;
+}
+
+int launch_pair(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
+                cudaStream_t stream) {
+    using Cfg = TileCfg<256, 32, true>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<256, 32, true, true>, p, ma, mb);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return static_cast<int>(e);
+}
+
 int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& ma,
              const CUtensorMap& mb, int grid, cudaStream_t stream) {
 #define B200_CASE(BN_)                                                                     \
@@ -194,6 +246,7 @@ int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 struct Plan {
     int bn, bk, split_k, kb_per_split, kblocks, tiles_m, tiles_n;
     bool tma;
+    bool pair;  // CTA-pair kernel: 256-row tiles
 };
 
 Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64_t K, bool tma_ok,
@@ -204,30 +257,45 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     pl.tiles_m = ceil_div(M, kBM);
     const int sms = st.sm_count > 0 ? st.sm_count : 148;
     int bn = 32;
+    bool pair = false;
+    const bool pair_legal = pl.tma && pl.bk == 32 && M > kBM && g_opt.pair_mode != 1;
     if (g_opt.tile_n == 32 || g_opt.tile_n == 64 || g_opt.tile_n == 128 || g_opt.tile_n == 256) {
         bn = static_cast<int>(g_opt.tile_n);
+        pair = pair_legal && bn == 256 && g_opt.pair_mode == 2;
     } else {
-        // Score = tensor-core rate of the tile width (wider MMAs amortise the A-operand reads,
-        // measured 1 : 0.68 : 0.4 : 0.22) x how full the last wave of tiles is.  Narrow
-        // products get narrow tiles instead of padding (N = 8, 10, 16, 24 run 32 wide).
-        const int cand[4] = {256, 128, 64, 32};
-        const double rate[4] = {1.0, 0.68, 0.40, 0.22};
+        // Score = measured relative rate of the tile shape (wider MMAs amortise the A-operand
+        // fetches; CTA pairs also halve each CTA's share of B) x the useful fraction of the
+        // tile x how full the last wave of tiles is.  Narrow products get narrow tiles instead
+        // of padding (N = 8, 10, 16, 24 run 32 wide).
+        const int cand[5] = {256, 256, 128, 64, 32};
+        const bool cand_pair[5] = {true, false, false, false, false};
+        const double rate[5] = {1.30, 1.0, 0.68, 0.40, 0.22};
         double best = -1.0;
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 5; ++i) {
             const int c = cand[i];
+            if (cand_pair[i] && !pair_legal) continue;
+            if (!cand_pair[i] && g_opt.pair_mode == 2 && pair_legal && N > 128) continue;
             if (c > 32 && N <= c / 2) continue;  // more than half the tile would be padding
-            const int64_t tiles = batch * pl.tiles_m * static_cast<int64_t>(ceil_div(N, c));
-            const int64_t waves = (tiles + sms - 1) / sms;
-            const double useful = static_cast<double>(N) / (static_cast<double>(ceil_div(N, c)) * c);
+            const int rows = cand_pair[i] ? 2 * kBM : kBM;
+            const int units = cand_pair[i] ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
+            const int64_t tm = ceil_div(M, rows), tn = ceil_div(N, c);
+            const int64_t tiles = batch * tm * tn;
+            const int64_t waves = (tiles + units - 1) / units;
+            const double useful = (static_cast<double>(N) / (static_cast<double>(tn) * c)) *
+                                  (static_cast<double>(M) / (static_cast<double>(tm) * rows));
             const double score = rate[i] * useful * static_cast<double>(tiles) /
-                                 static_cast<double>(waves * sms);
+                                 static_cast<double>(waves * units);
             if (score > best) {
                 best = score;
                 bn = c;
+                pair = cand_pair[i];
             }
         }
     }
     pl.bn = bn;
+    // Large products run on CTA pairs (256 x 256 tiles, two SMs per tile).
+    pl.pair = pair;
+    if (pl.pair) pl.tiles_m = ceil_div(M, 2 * kBM);
     pl.tiles_n = ceil_div(N, bn);
     pl.kblocks = ceil_div(K, pl.bk);
     // Deterministic split-K for tall-skinny products (few output tiles, long K).
@@ -235,9 +303,9 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     pl.kb_per_split = pl.kblocks;
     const int64_t tiles = batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n);
     int want = 1;
-    if (g_opt.split_k > 1) {
+    if (g_opt.split_k > 1 && !pl.pair) {
         want = static_cast<int>(g_opt.split_k);
-    } else if (g_opt.split_k == 0 && tiles * 2 <= sms && pl.kblocks >= 8) {
+    } else if (g_opt.split_k == 0 && !pl.pair && tiles * 2 <= sms && pl.kblocks >= 8) {
         want = static_cast<int>(sms / tiles);
         if (want > pl.kblocks / 4) want = pl.kblocks / 4;
     }
@@ -345,7 +413,8 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         if (rc) return rc;
         rc = make_operand_map(&oa, A, a_k_contig, M, K, lda, strideA, batch, kBM, pl.bk);
         if (rc) return rc;
-        rc = make_operand_map(&ob, B, b_k_contig, N, K, ldb, strideB, batch, pl.bn, pl.bk);
+        rc = make_operand_map(&ob, B, b_k_contig, N, K, ldb, strideB, batch,
+                              pl.pair ? pl.bn / 2 : pl.bn, pl.bk);
         if (rc) return rc;
         p.a_lbo = oa.lbo;
         p.a_sbo = oa.sbo;
@@ -355,7 +424,8 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         p.b_sbo = ob.sbo;
         p.b_kstep = ob.kstep;
         p.b_layout = ob.layout;
-        p.idesc = make_idesc_tf32(kBM, pl.bn, a_k_contig ? 0 : 1, b_k_contig ? 0 : 1);
+        p.idesc = make_idesc_tf32(pl.pair ? 2 * kBM : kBM, pl.bn, a_k_contig ? 0 : 1,
+                                  b_k_contig ? 0 : 1);
     } else {
         // the register-staged loader always writes K-major 128-byte-swizzled tiles
         p.a_lbo = p.b_lbo = 16;
@@ -365,8 +435,18 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         p.idesc = make_idesc_tf32(kBM, pl.bn, 0, 0);
     }
 
-    const int grid = static_cast<int>(total < st.sm_count ? total : st.sm_count);
-    int rc = dispatch(pl.bn, pl.bk, pl.tma, p, oa.map, ob.map, grid, stream);
+    int rc;
+    if (pl.pair) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int clusters = max_pair_clusters(dev);
+        if (clusters <= 0) return B200_EDEVICE;
+        if (clusters > total) clusters = static_cast<int>(total);
+        rc = launch_pair(p, oa.map, ob.map, clusters, stream);
+    } else {
+        const int grid = static_cast<int>(total < st.sm_count ? total : st.sm_count);
+        rc = dispatch(pl.bn, pl.bk, pl.tma, p, oa.map, ob.map, grid, stream);
+    }
     if (rc) return rc;
     if (pl.split_k > 1) {
         const int64_t elems = batch * M * N;
@@ -530,6 +610,9 @@ int b200_gemm_set_option(const char* name, long value) {
         g_opt.promote_every = value;
     } else if (!std::strcmp(name, "force_ldg")) {
         g_opt.force_ldg = value ? 1 : 0;
+    } else if (!std::strcmp(name, "pair_mode")) {
+        if (value < 0 || value > 2) return B200_EINVAL;
+        g_opt.pair_mode = value;
     } else if (!std::strcmp(name, "k_block")) {
         if (value != 16 && value != 32) return B200_EINVAL;
         g_opt.k_block = value;

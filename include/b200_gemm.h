@@ -106,7 +106,9 @@ uint64_t b200_gemm_launch_count(void);
  *   "split_k"       0 = automatic, 1 = never split, n = force n splits (needs workspace)
  *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
- *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path */
+ *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path
+ *   "pair_mode"     0 = automatic, 1 = never, 2 = whenever legal: run 256 x 256 tiles on pairs of
+ *                   CTAs (tcgen05 cta_group::2) */
 int b200_gemm_set_option(const char* name, long value);
 
 /* Static description of a code, never NULL. */

@@ -179,6 +179,48 @@ def test_every_tile_config_and_loader(pkg, orc, cuda, tile_n, loader):
     assert np.array_equal(got, orc.matmul(a, b))
 
 
+@pytest.mark.parametrize("form", ["NN", "NT", "TN", "TT"])
+@pytest.mark.parametrize("M,K,N", [(256, 32, 256), (300, 100, 520), (770, 260, 1000)])
+def test_cta_pair_kernel_exact(pkg, orc, cuda, form, M, K, N):
+    """The 256 x 256 CTA-pair kernel, forced on for shapes the planner would give to the
+    single-CTA kernel: integer inputs must come out exactly, in every transposition."""
+    import torch
+
+    rng = np.random.default_rng(M + N)
+    tA, tB = form[0] == "T", form[1] == "T"
+    a = rng.integers(-4, 5, size=(K, M) if tA else (M, K)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(N, K) if tB else (K, N)).astype(np.float32)
+    want = orc.matmul(np.ascontiguousarray(a.T) if tA else a, np.ascontiguousarray(b.T) if tB else b)
+    C = torch.full((M, N), float("nan"), device=cuda)
+    pkg.set_option("pair_mode", 2)
+    try:
+        gemm(pkg, cuda, dev(a, cuda), dev(b, cuda), C, batch=1, M=M, N=N, K=K, transA=tA, transB=tB,
+             lda=a.shape[1], ldb=b.shape[1], ldc=N)
+    finally:
+        pkg.set_option("pair_mode", 0)
+    assert np.array_equal(C.cpu().numpy(), want)
+
+
+def test_pair_and_single_kernels_agree_bitwise(pkg, orc, cuda):
+    """Both kernels sum every output element in the same order (k-blocks of 32, correction
+    products first), so their results are identical, not merely close."""
+    import torch
+
+    g = orc.Rng(31)
+    M, K, N = 512, 384, 768
+    A, B = dev(g.randn((M, K)), cuda), dev(g.randn((K, N)), cuda)
+    outs = []
+    for mode in (1, 2):
+        pkg.set_option("pair_mode", mode)
+        try:
+            C = torch.empty((M, N), device=cuda)
+            gemm(pkg, cuda, A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N)
+            outs.append(C)
+        finally:
+            pkg.set_option("pair_mode", 0)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_golden_pytorch_vectors_forward(pkg, cuda, golden_dir):
     """tests/test_reference.cpp:99-114, abs tolerance 1e-4."""
     z = np.load(golden_dir / "pytorch_matmul.npz")
