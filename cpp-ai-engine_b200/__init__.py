@@ -18,6 +18,7 @@ from .lib import (  # noqa: F401
     PRECISION_TF32,
     gemm,
     gemm_colshard,
+    gemm_static_scratch,
     launch_count,
     lib_path,
     load,

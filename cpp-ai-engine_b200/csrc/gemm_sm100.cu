@@ -461,6 +461,57 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     return rc;
 }
 
+// ------------------------------------------------------------------------------------------
+// Allocation-free entry point: scratch and status live in the library's own device image.
+// ------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB per GPU that loads the library
+
+// Split-K partial sums of b200_gemm_f32_static_scratch.  Shared by every call on the device
+// and never cleared: the GEMM kernel overwrites every partial the reduction later reads.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+// Bits of bounded waits that ran out in launches of that entry point (starts at zero).
+static __device__ int g_static_status;
+
+struct StaticState {
+    bool ready = false;
+    void* scratch = nullptr;  // device address of g_static_scratch on this device
+    DeviceState st;           // sm_count + status pointer, no owned allocations
+};
+StaticState g_static[kMaxDevices];
+
+// In host code the two symbols above are host-side stand-ins, not device addresses: the
+// address a kernel may use has to be asked for, once per device, with that device current.
+int static_state(StaticState** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return B200_EDEVICE;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    StaticState& ss = g_static[dev];
+    if (!ss.ready) {
+        int major = 0, sms = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+            return static_cast<int>(e);
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+            return static_cast<int>(e);
+        if (major != 10) return B200_EDEVICE;
+        void* scratch = nullptr;
+        void* status = nullptr;
+        if ((e = cudaGetSymbolAddress(&scratch, g_static_scratch)) != cudaSuccess)
+            return static_cast<int>(e);
+        if ((e = cudaGetSymbolAddress(&status, g_static_status)) != cudaSuccess)
+            return static_cast<int>(e);
+        ss.scratch = scratch;
+        ss.st.status = static_cast<int*>(status);
+        ss.st.cc_major = major;
+        ss.st.sm_count = sms;
+        ss.st.ready = true;
+        ss.ready = true;
+    }
+    *out = &ss;
+    return 0;
+}
+
 int grow(void** ptr, size_t* cap, size_t need) {
     if (need <= *cap) return 0;
     if (*ptr) cudaFree(*ptr);
@@ -578,6 +629,36 @@ int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, i
                      static_cast<cudaStream_t>(stream));
 }
 
+int b200_gemm_f32_static_scratch(const float* A, const float* B, float* C, int64_t batch, int64_t M,
+                                 int64_t N, int64_t K, int transA, int transB, int64_t lda,
+                                 int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB,
+                                 int64_t strideC, float alpha, float beta, int precision,
+                                 int* device_status, void* stream) {
+    StaticState* ss = nullptr;
+    int rc = static_state(&ss);
+    if (rc) return rc;
+    if (C == nullptr) return B200_EINVAL;
+    if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
+    if (batch == 1 && strideC == 0) strideC = M * ldc;
+    // The same plan the allocating entry point would make with ample workspace; refuse what
+    // the fixed scratch cannot hold rather than silently running a different plan.
+    if (batch > 0 && M > 0 && N > 0 && K > 0) {
+        const bool tma_ok = A != nullptr && B != nullptr && tma_legal(A, lda, strideA, batch) &&
+                            tma_legal(B, ldb, strideB, batch);
+        const Plan pl = make_plan(ss->st, batch, M, N, K, tma_ok, static_cast<size_t>(-1));
+        if (pl.split_k > 1) {
+            const size_t need = static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float);
+            if (need > kStaticScratchBytes) return B200_ENOSPACE;
+        }
+    }
+    DeviceState st = ss->st;  // plain copy: holds no allocation
+    if (device_status != nullptr) st.status = device_status;
+    float* dest[1] = {C};
+    return gemm_impl(st, A, B, dest, 1, batch, M, N, K, transA, transB, lda, ldb, ldc, strideA,
+                     strideB, strideC, alpha, beta, precision, ss->scratch, kStaticScratchBytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
 int b200_gemm_status(void) {
     DeviceState* st = nullptr;
     int rc = device_state(&st);
@@ -627,7 +708,7 @@ const char* b200_gemm_strerror(int code) {
         case B200_OK: return "success";
         case B200_EINVAL: return "invalid argument (shape, stride, flag or null pointer)";
         case B200_ERANGE: return "dimension out of the range the kernels index";
-        case B200_ENOSPACE: return "workspace too small";
+        case B200_ENOSPACE: return "scratch too small for this shape (the fixed 4 MiB of b200_gemm_f32_static_scratch)";
         case B200_EDEVICE: return "no sm_100 device, or the driver lacks cuTensorMapEncodeTiled";
         case B200_ETIMEDOUT: return "a bounded device-side wait ran out";
         default: break;

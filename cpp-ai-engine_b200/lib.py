@@ -24,6 +24,7 @@ EXPORTS = (
     "b200_matmul_f32",
     "b200_matmul_f32_host",
     "b200_gemm_f32_colshard",
+    "b200_gemm_f32_static_scratch",
     "b200_gemm_status",
     "b200_gemm_launch_count",
     "b200_gemm_set_option",
@@ -67,6 +68,10 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_f32_colshard.restype = c_int
     lib.b200_gemm_f32_colshard.argtypes = [c_vp, c_vp, ctypes.POINTER(c_vp), c_int, c_i64, c_i64,
                                            c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_vp]
+    lib.b200_gemm_f32_static_scratch.restype = c_int
+    lib.b200_gemm_f32_static_scratch.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
+                                                 c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f,
+                                                 c_int, c_vp, c_vp]
     lib.b200_gemm_status.restype = c_int
     lib.b200_gemm_status.argtypes = []
     lib.b200_gemm_launch_count.restype = ctypes.c_uint64
@@ -111,6 +116,20 @@ def gemm(A, B, C, *, batch: int, M: int, N: int, K: int, transA: bool = False, t
                               lda, ldb, ldc, strideA, strideB, strideC, alpha, beta, precision,
                               _ptr(workspace), workspace_bytes, _stream_ptr(stream))
     _check(rc, "b200_gemm_f32")
+
+
+def gemm_static_scratch(A, B, C, *, batch: int, M: int, N: int, K: int, transA: bool = False,
+                        transB: bool = False, lda: int, ldb: int, ldc: int, strideA: int = 0,
+                        strideB: int = 0, strideC: int = 0, alpha: float = 1.0, beta: float = 0.0,
+                        precision: int = PRECISION_3XTF32, device_status=None, stream=None) -> None:
+    """Same product as :func:`gemm` through ``b200_gemm_f32_static_scratch``: the split-K scratch
+    is the fixed array inside the library, nothing is allocated.  ``device_status`` is an optional
+    int32 CUDA tensor (zeroed by the caller) that receives device-side timeout bits."""
+    rc = load().b200_gemm_f32_static_scratch(_ptr(A), _ptr(B), _ptr(C), batch, M, N, K, int(transA),
+                                             int(transB), lda, ldb, ldc, strideA, strideB, strideC,
+                                             alpha, beta, precision, _ptr(device_status),
+                                             _stream_ptr(stream))
+    _check(rc, "b200_gemm_f32_static_scratch")
 
 
 def workspace_bytes(batch: int, M: int, N: int, K: int) -> int:

@@ -94,6 +94,40 @@ int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, i
                            int64_t M, int64_t N, int64_t K, int64_t col0, int64_t cols, int64_t lda,
                            int64_t ldb, int64_t ldc, int precision, void* stream);
 
+/* b200_gemm_f32 for callers that must not allocate device memory.  (No counterpart in the
+ * reference: its split-K path always takes its partials from a growable scratch buffer,
+ * src/cuda/kernels.cu:593-604.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits — inside a stream capture, in a
+ * real-time or memory-budgeted process whose device memory was handed out once at start-up, or
+ * under an allocator that owns the whole GPU and offers no hook for a library to ask for more.
+ * Such a caller can still pass A, B and C, but has nowhere to get the scratch that the
+ * deterministic split-K path (tall-skinny products such as dW = X^T x dY) writes its partial
+ * sums to.  Here that scratch is a fixed 4 MiB array inside the library's device image, present on
+ * every GPU that loads the library until the process exits.  The call performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ *
+ * Same arguments and arithmetic as b200_gemm_f32; results are identical to it when it is given
+ * ample workspace.  Differences:
+ *   - a shape whose split-K plan needs more than 4 MiB of partials is refused with
+ *     B200_ENOSPACE (the automatic plan never needs more than about 2.4 MB on a B200; forced
+ *     "split_k" / "tile_n" options can);
+ *   - device_status: optional DEVICE pointer to an int, zeroed by the caller, that receives the
+ *     bits of any bounded device-side wait that ran out (non-zero = treat results as invalid).
+ *     With NULL those bits go to a word inside the library that b200_gemm_status does not read;
+ *   - the first call on each device looks up the device addresses of the library's scratch and
+ *     status word.  Make that first call with the device current and before any stream capture
+ *     begins;
+ *   - all calls on a device share the one scratch array, which keeps whatever the last call left
+ *     in it (nothing in it needs to start at zero).  Two calls that may run at the same time on
+ *     one GPU — different streams, or different threads — race on it: keep such calls on one
+ *     stream or order them yourself. */
+int b200_gemm_f32_static_scratch(const float* A, const float* B, float* C, int64_t batch, int64_t M,
+                                 int64_t N, int64_t K, int transA, int transB, int64_t lda,
+                                 int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB,
+                                 int64_t strideC, float alpha, float beta, int precision,
+                                 int* device_status, void* stream);
+
 /* Device-side health of the launches so far on the current device: synchronises the device,
  * returns 0 or B200_ETIMEDOUT if any bounded wait inside a kernel ran out, and clears the flag. */
 int b200_gemm_status(void);
