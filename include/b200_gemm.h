@@ -98,9 +98,10 @@ int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, i
  * reference: its split-K path always takes its partials from a growable scratch buffer,
  * src/cuda/kernels.cu:593-604.)
  *
- * Who needs it: code that runs where cudaMalloc is off limits — inside a stream capture, in a
- * real-time or memory-budgeted process whose device memory was handed out once at start-up, or
- * under an allocator that owns the whole GPU and offers no hook for a library to ask for more.
+ * Who needs it: code that runs where cudaMalloc is off limits — a latency-critical loop that
+ * cannot take cudaMalloc's implicit device synchronisation, a memory-budgeted process whose
+ * device memory was handed out once at start-up, or a program under an arena allocator that
+ * owns the whole GPU and offers no hook for a library to ask for more.
  * Such a caller can still pass A, B and C, but has nowhere to get the scratch that the
  * deterministic split-K path (tall-skinny products such as dW = X^T x dY) writes its partial
  * sums to.  Here that scratch is a fixed 4 MiB array inside the library's device image, present on

@@ -1,7 +1,7 @@
 """The allocation-free entry point ``b200_gemm_f32_static_scratch``.
 
-Some callers cannot call cudaMalloc when they need a product: they are inside a stream capture,
-or they run under an allocator that was given the whole GPU at start-up.  For them the library
+Some callers cannot call cudaMalloc when they need a product: their loop cannot afford the
+implicit synchronisation, or they run under an allocator that was given the whole GPU at start-up.  For them the library
 carries its split-K scratch as a fixed array in its own device image.  This test calls that
 entry point through the C ABI on shapes that take the split-K path, twice in a row with
 different inputs (the second call finds the first call's partial sums still in the scratch),
