@@ -1,0 +1,174 @@
+// C++17 host side of the B200 matmul path: the slice of the reference engine's public
+// surface that its matrix product lives behind, re-stated over the C ABI in
+// include/b200_gemm.h.  Same names, argument meaning and error behaviour as the reference:
+//
+//   engine::manual_seed / Tensor::rand / Tensor::randn    src/tensor.cpp:24-31, 117-135
+//   engine::Storage  (host vector + lazy device mirror)   include/engine/detail/storage.hpp:99-117
+//   engine::cuda::ops::matmul (the device seam)           include/engine/detail/cuda_ops.hpp:46-47
+//   engine::cuda::transfer_stats / kernels_launched       include/engine/cuda.hpp:79-81, 209-218
+//   engine::Tensor::matmul / transpose / reshape /        include/engine/tensor.hpp:157-198,
+//           backward / grad                               src/tensor_ops.cpp:475-588
+//
+// What differs, on purpose: there is no CPU loop (ops::matmul never returns false — it throws
+// when the device cannot run the product), transpose() is a zero-copy view that the product
+// consumes as a layout flag instead of a materialised buffer, and the backward pass calls the
+// transposed forms directly.
+#ifndef ENGINE_B200_HPP
+#define ENGINE_B200_HPP
+
+#include <cstddef>
+#include <cstdint>
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace engine {
+
+void manual_seed(uint64_t seed);
+
+// A tensor's buffer and which side of the bus holds the valid copy.  Invariant: at least one
+// of the two copies is valid at all times.
+class Storage {
+public:
+    Storage();
+    Storage(size_t count, float fill);
+    explicit Storage(std::vector<float> values);
+
+    size_t size() const { return buf_->count; }
+    bool empty() const { return buf_->count == 0; }
+
+    const std::vector<float>& host() const;  // downloads if the host copy is stale
+    std::vector<float>& host_mut();          // same, and marks the device copy stale
+
+    const float* device() const;  // uploads if the device copy is stale
+    float* device_mut();          // same, and marks the host copy stale
+    float* device_write();        // allocates without uploading; the kernel overwrites all of it
+    void revert_device_write();   // undoes a device_write() whose kernel never launched
+    bool resident_on_device() const { return buf_->device_valid; }
+
+    Storage clone() const;  // independent copy that stays on whichever side the values live
+    Storage share() const;  // second handle on the same buffer (what makes reshape a view)
+    bool shares_with(const Storage& other) const { return buf_ == other.buf_; }
+
+private:
+    struct Buffer {
+        std::vector<float> host;
+        size_t count = 0;
+        float fill = 0.0f;
+        float* device = nullptr;
+        bool host_valid = true;
+        bool device_valid = false;
+        bool reverted_host_valid = true;
+        ~Buffer();
+    };
+    void materialise() const;
+    void ensure_device_buffer() const;
+    std::shared_ptr<Buffer> buf_;
+};
+
+namespace cuda {
+
+bool available();
+void synchronize();
+
+struct TransferStats {
+    size_t to_device_bytes = 0;
+    size_t to_host_bytes = 0;
+    size_t to_device_count = 0;
+    size_t to_host_count = 0;
+};
+TransferStats transfer_stats();
+void reset_transfer_stats();
+size_t kernels_launched();
+
+// Reduced precision is opt-in and never selected automatically (include/engine/cuda.hpp:153-177).
+enum class MatmulKernel { Auto, TensorCore };
+void set_matmul_kernel(MatmulKernel kernel);
+MatmulKernel matmul_kernel();
+
+// Throws std::runtime_error if a bounded device-side wait ran out in an earlier launch.
+void check_device_status();
+
+namespace ops {
+
+// out = a x b + beta * out, batched; an unbatched operand is reused for every batch element.
+// Returns true when the device did the work.  It always does, or throws std::runtime_error:
+// there is no CPU path for the caller to fall back to.
+bool matmul(const Storage& a, const Storage& b, Storage& out, size_t batch, size_t rows,
+            size_t inner_dim, size_t cols, bool a_batched, bool b_batched, float beta = 0.0f);
+
+// The same with operands that are stored transposed (a as inner_dim x rows, b as cols x
+// inner_dim per batch element).  No reference counterpart: the reference materialises the
+// transpose first (src/tensor_ops.cpp:576, :581).
+bool matmul_ex(const Storage& a, const Storage& b, Storage& out, size_t batch, size_t rows,
+               size_t inner_dim, size_t cols, bool a_batched, bool b_batched, bool a_transposed,
+               bool b_transposed, float beta = 0.0f);
+
+}  // namespace ops
+}  // namespace cuda
+
+struct TensorImpl;
+
+class Tensor {
+public:
+    Tensor();
+    explicit Tensor(const std::vector<size_t>& shape, float fill_value = 0.0f,
+                    bool requires_grad = false);
+    Tensor(const std::vector<size_t>& shape, const std::vector<float>& data,
+           bool requires_grad = false);
+
+    static Tensor zeros(const std::vector<size_t>& shape, bool requires_grad = false);
+    static Tensor ones(const std::vector<size_t>& shape, bool requires_grad = false);
+    static Tensor rand(const std::vector<size_t>& shape, float min_val = -1.0f, float max_val = 1.0f,
+                       bool requires_grad = false);
+    static Tensor randn(const std::vector<size_t>& shape, float mean = 0.0f, float stddev = 1.0f,
+                        bool requires_grad = false);
+
+    bool requires_grad() const;
+    void set_requires_grad(bool requires_grad);
+    Tensor grad() const;
+    bool has_grad() const;
+    void zero_grad();
+    void add_grad(const Tensor& g);
+    void backward();
+    void backward(const Tensor& grad_output);
+
+    const std::vector<size_t>& shape() const;
+    size_t ndim() const;
+    size_t size() const;
+    std::string shape_str() const;
+
+    // The elements in logical row-major order.  Reading downloads if the values live on the
+    // device; on a transposed view the copy is made in logical order.
+    std::vector<float> to_vector() const;
+    float at(size_t flat_index) const;
+    float operator()(size_t row, size_t col) const;
+
+    // (M, K) x (K, N) -> (M, N); (B..., M, K) x (B..., K, N) -> (B..., M, N); a 2-D operand is
+    // shared by every matrix of the other's batch.  Throws std::invalid_argument exactly where
+    // the reference does (src/tensor_ops.cpp:476-503).
+    Tensor matmul(const Tensor& other) const;
+    // Swaps the last two axes.  A view: no data moves; a product consumes it as a layout flag.
+    Tensor transpose() const;
+    // Same elements, new shape (a view of a non-transposed tensor, a copy of a transposed one).
+    Tensor reshape(const std::vector<size_t>& new_shape) const;
+    Tensor detach() const;
+
+    bool resident_on_device() const;
+    bool is_transposed_view() const;
+
+private:
+    explicit Tensor(std::shared_ptr<TensorImpl> impl);
+    std::shared_ptr<TensorImpl> impl_;
+    friend struct TensorImpl;
+};
+
+// Reads every tensor of a file in the reference's documented container format
+// (include/engine/serialize.hpp:12-31: "CPPAIENG", u32 version, u32 count, then per tensor
+// u32 name length, name, u32 ndim, u64 dims, f32 data; little-endian).
+std::vector<std::pair<std::string, Tensor>> load_tensors(const std::string& path);
+
+}  // namespace engine
+
+#endif  // ENGINE_B200_HPP

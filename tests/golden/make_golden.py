@@ -4,7 +4,7 @@ reference tree and the reference CPU build oracle/_ref are present):
     python tests/golden/make_golden.py [--reference /root/reference]
 
 Outputs (small, committed):
-  pytorch_matmul.npz   the reference's own PyTorch golden vectors for its matrix product and
+  pytorch_matmul.npz / .bin   the reference's own PyTorch golden vectors for its matrix product and
                        its gradients (tests/fixtures/matmul*.bin, consumed by
                        tests/test_reference.cpp:99-114), re-encoded as npz.
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
@@ -56,6 +56,19 @@ def read_fixture(path: Path) -> dict:
         out[name] = np.frombuffer(raw, dtype="<f4", count=n, offset=off).reshape(dims).copy()
         off += 4 * n
     return out
+
+
+def write_container(path: Path, tensors: dict) -> None:
+    """Writes tensors in the same documented container format (version 1, little-endian)."""
+    out = bytearray(b"CPPAIENG")
+    out += struct.pack("<II", 1, len(tensors))
+    for name, val in tensors.items():
+        val = np.ascontiguousarray(val, dtype="<f4")
+        raw_name = name.encode()
+        out += struct.pack("<I", len(raw_name)) + raw_name
+        out += struct.pack("<I", val.ndim) + struct.pack(f"<{val.ndim}Q", *val.shape)
+        out += val.tobytes()
+    path.write_bytes(bytes(out))
 
 
 def sha(x: np.ndarray) -> str:
@@ -129,6 +142,7 @@ def main() -> None:
         for key, val in fx.items():
             packed[f"{name}/{key}"] = val
     np.savez(HERE / "pytorch_matmul.npz", **packed)
+    write_container(HERE / "pytorch_matmul.bin", packed)  # same vectors for the C++ host tests
 
     # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
     known = [
