@@ -93,9 +93,10 @@ struct TileCfg {
     static constexpr uint32_t kBBytes = kBCols * BK * 4;
     static constexpr uint32_t kHalf = kABytes + kBBytes;  // raw / head tiles; tails follow
     static constexpr uint32_t kStageBytes = 2 * kHalf;
-    static constexpr int kMaxStages = (227 * 1024 - 2048) / kStageBytes;
+    static constexpr int kMaxStages = (227 * 1024 - 2048 - kWorkerWarps * 4096) / kStageBytes;
     static constexpr int kStages = kMaxStages > 4 ? 4 : kMaxStages;
-    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+    static constexpr uint32_t kEpilogueBytes = kWorkerWarps * 4096;  // one 32 x 32 block per warp
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpilogueBytes + 1024;  // + alignment slack
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;           // two accumulators
     static constexpr int kCols = BN / 2;                                  // columns per worker
 };
@@ -595,52 +596,73 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             ++chain;
 
             // ---------------------------------------------------------------- epilogue
-            const int row = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
-            const int col0 = wk.nt * BN + half * kCols;
-            if (row < p.M && col0 < p.N) {
-                if (p.split_k > 1) {
-                    float* crow = p.partial +
-                                  (((long long)wk.sp * p.batch + wk.b) * p.M + row) * (long long)p.N;
-                    const bool vec = (p.N & 3) == 0;
+            // A thread holds kCols consecutive columns of ONE row; stored as it stands, every
+            // store instruction of a warp would touch 32 different rows with 16 bytes each.
+            // Each warp therefore turns 32 x 32 blocks through its own 4 KB of shared memory
+            // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores rows:
+            // one instruction writes four full 128-byte row segments — what HBM and, for the
+            // peers' copies of C, NVLink want.
+            {
+                float4* tile = reinterpret_cast<float4*>(smem + kStages * Cfg::kStageBytes) + wid * 256;
+                const int row_base = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32;
+                const int col_base = wk.nt * BN + half * kCols;
+                const int sub_row = lane >> 3;   // row within a group of four
+                const int chunk = lane & 7;      // 16-byte chunk of the 128-byte row segment
+                const bool split_out = p.split_k > 1;
+                const float alpha = split_out ? 1.0f : p.alpha;
+                const float beta = split_out ? 0.0f : p.beta;
+                const long long ld_out = split_out ? (long long)p.N : p.ldc;
+                const bool vec = split_out ? ((p.N & 3) == 0) : (p.c_vec_ok != 0);
+                const int n_out = split_out ? 1 : p.n_dest;
+                const long long base_off =
+                    split_out ? ((long long)wk.sp * p.batch + wk.b) * (long long)p.M * p.N
+                              : (long long)wk.b * p.strideC;
 #pragma unroll
-                    for (int j = 0; j < kCols; j += 4) {
-                        const int col = col0 + j;
-                        if (vec && col + 3 < p.N) {
-                            *reinterpret_cast<float4*>(crow + col) =
-                                make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                        } else {
+                for (int g = 0; g < kCols / 32 + (kCols < 32 ? 1 : 0); ++g) {
+                    constexpr int kChunkCols = kCols < 32 ? kCols : 32;
+                    constexpr int kChunks = kChunkCols / 4;
+                    __syncwarp();
 #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < p.N) crow[col + e] = acc[j + e];
-                        }
+                    for (int j = 0; j < kChunks; ++j) {
+                        tile[lane * 8 + (j ^ (lane & 7))] =
+                            make_float4(acc[g * 32 + 4 * j], acc[g * 32 + 4 * j + 1],
+                                        acc[g * 32 + 4 * j + 2], acc[g * 32 + 4 * j + 3]);
                     }
-                } else {
-                    const float alpha = p.alpha, beta = p.beta;
-                    const long long coff = (long long)wk.b * p.strideC + (long long)row * p.ldc;
-                    const bool vec = p.c_vec_ok != 0;
-                    for (int dd = 0; dd < p.n_dest; ++dd) {
-                        float* crow = p.dest[dd] + coff;
+                    __syncwarp();
+                    const int col = col_base + g * 32 + chunk * 4;
+                    if (chunk < kChunks && col < p.N) {
 #pragma unroll
-                        for (int j = 0; j < kCols; j += 4) {
-                            const int col = col0 + j;
-                            if (vec && col + 3 < p.N) {
-                                float4 o = make_float4(alpha * acc[j], alpha * acc[j + 1],
-                                                       alpha * acc[j + 2], alpha * acc[j + 3]);
-                                if (beta != 0.f) {
-                                    const float4 old = *reinterpret_cast<const float4*>(crow + col);
-                                    o.x += beta * old.x;
-                                    o.y += beta * old.y;
-                                    o.z += beta * old.z;
-                                    o.w += beta * old.w;
-                                }
-                                *reinterpret_cast<float4*>(crow + col) = o;
-                            } else {
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + sub_row;
+                            const int row = row_base + rr;
+                            if (row >= p.M) continue;
+                            float4 v = tile[rr * 8 + (chunk ^ (rr & 7))];
+                            v.x *= alpha;
+                            v.y *= alpha;
+                            v.z *= alpha;
+                            v.w *= alpha;
+                            const long long off = base_off + (long long)row * ld_out + col;
+                            for (int dd = 0; dd < n_out; ++dd) {
+                                float* dst = (split_out ? p.partial : p.dest[dd]) + off;
+                                if (vec && col + 3 < p.N) {
+                                    float4 o = v;
+                                    if (beta != 0.f) {
+                                        const float4 old = *reinterpret_cast<const float4*>(dst);
+                                        o.x += beta * old.x;
+                                        o.y += beta * old.y;
+                                        o.z += beta * old.z;
+                                        o.w += beta * old.w;
+                                    }
+                                    *reinterpret_cast<float4*>(dst) = o;
+                                } else {
+                                    const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    if (col + e < p.N) {
-                                        float o = alpha * acc[j + e];
-                                        if (beta != 0.f) o += beta * crow[col + e];
-                                        crow[col + e] = o;
+                                    for (int e = 0; e < 4; ++e) {
+                                        if (col + e < p.N) {
+                                            float o = e4[e];
+                                            if (beta != 0.f) o += beta * dst[e];
+                                            dst[e] = o;
+                                        }
                                     }
                                 }
                             }

@@ -25,6 +25,10 @@ struct DeviceState {
     float* stage_c = nullptr;
     void* stage_ws = nullptr;
     size_t cap_a = 0, cap_b = 0, cap_c = 0, cap_ws = 0;
+    // streams and events of the pipelined host path (created on first use)
+    cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
+    cudaEvent_t ev_a[16] = {}, ev_b[16] = {}, ev_c[256] = {};
+    bool pipe_ready = false;
 };
 
 std::mutex g_mutex;
@@ -38,6 +42,7 @@ struct Options {
     long force_ldg = 0;
     long k_block = 32;
     long pair_mode = 0;  // 0 automatic, 1 never, 2 whenever legal
+    long host_pipeline = 1;  // b200_matmul_f32_host: overlap transfers with the math
 };
 Options g_opt;
 #ifdef B200_PHASE_PROFILE
@@ -523,6 +528,95 @@ int grow(void** ptr, size_t* cap, size_t need) {
     return 0;
 }
 
+
+// One large product from host buffers as a 2-D wavefront of blocks: row panels of A and column
+// panels of B are uploaded alternately (A_0, B_0, A_1, B_1, ...); block C(i,j) is multiplied
+// as soon as A_i and B_j are on the device and downloaded as soon as it is done.  Uploads,
+// kernels and downloads run on three streams, so the bus works in both directions under the
+// math instead of before and after it.  Overlap needs page-locked host buffers; with pageable
+// ones the copies serialise but the result is the same.
+int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, int64_t M, int64_t K,
+                   int64_t N) {
+    cudaError_t e;
+    if (!st.pipe_ready) {
+        if ((e = cudaStreamCreateWithFlags(&st.s_h2d, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&st.s_comp, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&st.s_d2h, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        for (auto& ev : st.ev_a)
+            if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return e;
+        for (auto& ev : st.ev_b)
+            if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return e;
+        for (auto& ev : st.ev_c)
+            if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return e;
+        st.pipe_ready = true;
+    }
+    // panels of whole 256-row / 256-column tiles: at most 8 x 8 blocks, and no block smaller
+    // than 2048 x 2048 (64 tiles) so that every launch still fills most of the GPU
+    auto panel = [](int64_t dim) {
+        int64_t p = (dim + 7) / 8;
+        p = ((p + 255) / 256) * 256;
+        return p < 2048 ? static_cast<int64_t>(2048) : p;
+    };
+    const int64_t bm = panel(M), bn = panel(N);
+    const int pm = static_cast<int>((M + bm - 1) / bm), pn = static_cast<int>((N + bn - 1) / bn);
+    float* dA = st.stage_a;
+    float* dB = st.stage_b;
+    float* dC = st.stage_c;
+
+    auto upload_a = [&](int i) -> cudaError_t {
+        const int64_t r0 = i * bm, rows = std::min<int64_t>(bm, M - r0);
+        cudaError_t err = cudaMemcpyAsync(dA + r0 * K, a + r0 * K, static_cast<size_t>(rows) * K * 4,
+                                          cudaMemcpyHostToDevice, st.s_h2d);
+        return err != cudaSuccess ? err : cudaEventRecord(st.ev_a[i], st.s_h2d);
+    };
+    auto upload_b = [&](int j) -> cudaError_t {
+        const int64_t c0 = j * bn, cols = std::min<int64_t>(bn, N - c0);
+        cudaError_t err = cudaMemcpy2DAsync(dB + c0, static_cast<size_t>(N) * 4, b + c0,
+                                            static_cast<size_t>(N) * 4, static_cast<size_t>(cols) * 4,
+                                            static_cast<size_t>(K), cudaMemcpyHostToDevice, st.s_h2d);
+        return err != cudaSuccess ? err : cudaEventRecord(st.ev_b[j], st.s_h2d);
+    };
+    auto block = [&](int i, int j) -> int {
+        const int64_t r0 = i * bm, rows = std::min<int64_t>(bm, M - r0);
+        const int64_t c0 = j * bn, cols = std::min<int64_t>(bn, N - c0);
+        cudaError_t err;
+        if ((err = cudaStreamWaitEvent(st.s_comp, st.ev_a[i], 0)) != cudaSuccess) return err;
+        if ((err = cudaStreamWaitEvent(st.s_comp, st.ev_b[j], 0)) != cudaSuccess) return err;
+        float* dest[1] = {dC + r0 * N + c0};
+        int rc = gemm_impl(st, dA + r0 * K, dB + c0, dest, 1, 1, rows, cols, K, 0, 0, K, N, N, 0, 0,
+                           rows * N, 1.0f, 0.0f, B200_PRECISION_3XTF32, nullptr, 0, st.s_comp);
+        if (rc) return rc;
+        cudaEvent_t done = st.ev_c[i * pn + j];
+        if ((err = cudaEventRecord(done, st.s_comp)) != cudaSuccess) return err;
+        if ((err = cudaStreamWaitEvent(st.s_d2h, done, 0)) != cudaSuccess) return err;
+        err = cudaMemcpy2DAsync(out + r0 * N + c0, static_cast<size_t>(N) * 4, dC + r0 * N + c0,
+                                static_cast<size_t>(N) * 4, static_cast<size_t>(cols) * 4,
+                                static_cast<size_t>(rows), cudaMemcpyDeviceToHost, st.s_d2h);
+        return err;
+    };
+
+    const int steps = std::max(pm, pn);
+    for (int k = 0; k < steps; ++k) {
+        if (k < pm && (e = upload_a(k)) != cudaSuccess) return e;
+        if (k < pn && (e = upload_b(k)) != cudaSuccess) return e;
+        // blocks that became computable with the k-th pair of panels
+        if (k < pn)
+            for (int i = 0; i <= std::min(k, pm - 1); ++i) {
+                int rc = block(i, k);
+                if (rc) return rc;
+            }
+        if (k < pm)
+            for (int j = 0; j < std::min(k, pn); ++j) {
+                int rc = block(k, j);
+                if (rc) return rc;
+            }
+    }
+    if ((e = cudaStreamSynchronize(st.s_h2d)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(st.s_comp)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(st.s_d2h)) != cudaSuccess) return e;
+    return B200_OK;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -592,6 +686,12 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
         if ((rc = grow(reinterpret_cast<void**>(&st->stage_b), &st->cap_b, nb ? nb : 16))) return rc;
         if ((rc = grow(reinterpret_cast<void**>(&st->stage_c), &st->cap_c, nc))) return rc;
         if (nws && (rc = grow(&st->stage_ws, &st->cap_ws, nws))) return rc;
+    }
+    // Large single products overlap their transfers with the math, block by block.
+    if (batch == 1 && beta == 0.0f && rows >= 4096 && cols >= 4096 && inner_dim >= 512 &&
+        (cols % 4) == 0 && (inner_dim % 4) == 0 && g_opt.host_pipeline != 0) {
+        return host_wavefront(*st, a, b, out, static_cast<int64_t>(rows), static_cast<int64_t>(inner_dim),
+                              static_cast<int64_t>(cols));
     }
     cudaStream_t stream = nullptr;
     cudaError_t e;
@@ -691,6 +791,8 @@ int b200_gemm_set_option(const char* name, long value) {
         g_opt.promote_every = value;
     } else if (!std::strcmp(name, "force_ldg")) {
         g_opt.force_ldg = value ? 1 : 0;
+    } else if (!std::strcmp(name, "host_pipeline")) {
+        g_opt.host_pipeline = value ? 1 : 0;
     } else if (!std::strcmp(name, "pair_mode")) {
         if (value < 0 || value > 2) return B200_EINVAL;
         g_opt.pair_mode = value;

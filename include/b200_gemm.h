@@ -78,7 +78,10 @@ int b200_matmul_f32(const float* a, const float* b, float* out, size_t batch, si
 /* Same product from HOST buffers: uploads a and b, runs the kernel, downloads out, and returns
  * after the result is on the host — the whole cost a caller holding host tensors pays, as when
  * the reference's Storage uploads stale operands and a later data() downloads the result
- * (src/storage.cpp:281-307).  Device staging buffers are cached per device between calls. */
+ * (src/storage.cpp:281-307).  Device staging buffers are cached per device between calls.
+ * A large single product (rows, cols >= 4096) is run as a wavefront of blocks whose uploads,
+ * kernels and downloads overlap on three streams; pass page-locked host buffers to get the
+ * overlap (pageable ones work, serialised). */
 int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batch, size_t rows,
                          size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta);
 
@@ -142,6 +145,8 @@ uint64_t b200_gemm_launch_count(void);
  *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
  *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path
+ *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math, 0 = one
+ *                   upload, one kernel, one download
  *   "pair_mode"     0 = automatic, 1 = never, 2 = whenever legal: run 256 x 256 tiles on pairs of
  *                   CTAs (tcgen05 cta_group::2) */
 int b200_gemm_set_option(const char* name, long value);
