@@ -72,6 +72,8 @@ struct GemmParams {
     int precision;      // 0 = 3xTF32, 1 = TF32
     int promote_every;  // k-blocks per TMEM accumulation chain
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
+    int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
+    int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
     int* status;
     // tensor-core view of the shared-memory tiles
     uint32_t a_lbo, a_sbo, a_kstep, a_layout;
@@ -103,12 +105,14 @@ struct TileCfg {
 
 struct Work {
     int b, mt, nt, sp, kb0, kb1;
+    int tile;  // linear tile index (batch included)
 };
 
 __device__ __forceinline__ Work decode_work(const GemmParams& p, int w) {
     Work r;
     r.sp = w % p.split_k;
-    int t = w / p.split_k;
+    int t = w / p.split_k + p.tile_offset;
+    r.tile = t;
     const int tiles = p.tiles_m * p.tiles_n;
     r.b = t / tiles;
     t -= r.b * tiles;
@@ -611,12 +615,17 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const bool split_out = p.split_k > 1;
                 const float alpha = split_out ? 1.0f : p.alpha;
                 const float beta = split_out ? 0.0f : p.beta;
-                const long long ld_out = split_out ? (long long)p.N : p.ldc;
-                const bool vec = split_out ? ((p.N & 3) == 0) : (p.c_vec_ok != 0);
+                const bool compact = split_out && p.tail_tiles > 0;
+                const long long ld_out = compact ? (long long)BN : split_out ? (long long)p.N : p.ldc;
+                const bool vec = compact ? true : split_out ? ((p.N & 3) == 0) : (p.c_vec_ok != 0);
                 const int n_out = split_out ? 1 : p.n_dest;
+                // compact: element (row, col) of tail tile t lives at
+                //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
-                    split_out ? ((long long)wk.sp * p.batch + wk.b) * (long long)p.M * p.N
-                              : (long long)wk.b * p.strideC;
+                    compact ? (((long long)wk.sp * p.tail_tiles + (wk.tile - p.tile_offset)) * kTileM -
+                               (long long)wk.mt * kTileM) * BN - (long long)wk.nt * BN
+                    : split_out ? ((long long)wk.sp * p.batch + wk.b) * (long long)p.M * p.N
+                                : (long long)wk.b * p.strideC;
 #pragma unroll
                 for (int g = 0; g < kCols / 32 + (kCols < 32 ? 1 : 0); ++g) {
                     constexpr int kChunkCols = kCols < 32 ? kCols : 32;
@@ -710,6 +719,44 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* _
         float o = alpha * s;
         if (beta != 0.f) o += beta * *out;
         *out = o;
+    }
+}
+
+// Adds the compact split-K partials of the tail-wave tiles into C (ascending split order):
+// block x handles tile x / 8, rows [x % 8 * tile_rows / 8, ...).
+__global__ void tail_reduce_kernel(const GemmParams p, int tile_rows, int bn) {
+    const int tl = blockIdx.x >> 3;
+    const int slab = blockIdx.x & 7;
+    GemmParams q = p;
+    q.split_k = 1;
+    const Work wk = decode_work(q, tl);  // tile_offset is applied inside
+    const int rows_per = tile_rows / 8;
+    const int chunks = bn / 4;
+    const long long tile_elems = (long long)tile_rows * bn;
+    for (int i = threadIdx.x; i < rows_per * chunks; i += blockDim.x) {
+        const int r = slab * rows_per + i / chunks;
+        const int c4 = (i % chunks) * 4;
+        const int row = wk.mt * tile_rows + r;
+        const int col = wk.nt * bn + c4;
+        if (row >= p.M || col >= p.N) continue;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < p.split_k; ++sp) {
+            const float4 v = *reinterpret_cast<const float4*>(
+                p.partial + ((long long)sp * p.tail_tiles + tl) * tile_elems + (long long)r * bn + c4);
+            s.x += v.x;
+            s.y += v.y;
+            s.z += v.z;
+            s.w += v.w;
+        }
+        float* out = p.dest[0] + (long long)wk.b * p.strideC + (long long)row * p.ldc + col;
+        const float e4[4] = {s.x, s.y, s.z, s.w};
+        for (int e = 0; e < 4; ++e) {
+            if (col + e < p.N) {
+                float o = p.alpha * e4[e];
+                if (p.beta != 0.f) o += p.beta * out[e];
+                out[e] = o;
+            }
+        }
     }
 }
 

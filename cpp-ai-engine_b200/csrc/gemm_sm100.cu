@@ -43,6 +43,7 @@ struct Options {
     long k_block = 32;
     long pair_mode = 0;  // 0 automatic, 1 never, 2 whenever legal
     long host_pipeline = 1;  // b200_matmul_f32_host: overlap transfers with the math
+    long tail_split = 1;     // split the tiles of a mostly-empty last wave along K
 };
 Options g_opt;
 #ifdef B200_PHASE_PROFILE
@@ -252,6 +253,10 @@ struct Plan {
     int bn, bk, split_k, kb_per_split, kblocks, tiles_m, tiles_n;
     bool tma;
     bool pair;  // CTA-pair kernel: 256-row tiles
+    // Tail wave: when the tile count leaves the last wave mostly empty, the tiles of that wave
+    // are split along K (tail_split ways) in a second launch so that all SMs stay busy.
+    int full_tiles, tail_tiles, tail_split, tail_kb_per_split;
+    size_t tail_bytes;
 };
 
 Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64_t K, bool tma_ok,
@@ -324,6 +329,34 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
             pl.kb_per_split = per;
         }
     }
+    // Tail wave.  Example: 4096^3 is 256 pair tiles on 74 clusters = 3.46 waves; the last 34
+    // tiles run two-way split as 68 half-length items, so the launch pair takes 3.5 wave-times
+    // instead of 4.
+    pl.full_tiles = static_cast<int>(tiles);
+    pl.tail_tiles = 0;
+    pl.tail_split = 1;
+    pl.tail_kb_per_split = pl.kblocks;
+    pl.tail_bytes = 0;
+    if (pl.split_k == 1 && g_opt.tail_split != 0 && pl.kblocks >= 32 && pl.bn >= 128) {
+        const int units = pl.pair ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
+        const int64_t full = (tiles / units) * units;
+        const int64_t tail = tiles - full;
+        if (full > 0 && tail > 0 && tail * 10 <= units * 6) {
+            int split = static_cast<int>(units / tail);
+            if (split > 4) split = 4;
+            const int per = ceil_div(pl.kblocks, split);
+            split = ceil_div(pl.kblocks, per);
+            const size_t need = static_cast<size_t>(split) * tail * (pl.pair ? 2 * kBM : kBM) * pl.bn *
+                                sizeof(float);
+            if (split > 1 && workspace_bytes >= need) {
+                pl.full_tiles = static_cast<int>(full);
+                pl.tail_tiles = static_cast<int>(tail);
+                pl.tail_split = split;
+                pl.tail_kb_per_split = per;
+                pl.tail_bytes = need;
+            }
+        }
+    }
     return pl;
 }
 
@@ -362,7 +395,13 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
                          (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0)
                             ? workspace_bytes
                             : 0);
-    const int64_t total = batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n) * pl.split_k;
+    if (n_dest != 1) {  // the tail launch reduces into one C
+        pl.full_tiles = static_cast<int>(batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n));
+        pl.tail_tiles = 0;
+    }
+    const int64_t total = pl.tail_tiles > 0
+                              ? static_cast<int64_t>(pl.full_tiles)
+                              : batch * pl.tiles_m * static_cast<int64_t>(pl.tiles_n) * pl.split_k;
     if (total > 0x7fffffffll) return B200_ERANGE;
 
     GemmParams p{};
@@ -440,19 +479,34 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         p.idesc = make_idesc_tf32(kBM, pl.bn, 0, 0);
     }
 
-    int rc;
-    if (pl.pair) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        int clusters = max_pair_clusters(dev);
-        if (clusters <= 0) return B200_EDEVICE;
-        if (clusters > total) clusters = static_cast<int>(total);
-        rc = launch_pair(p, oa.map, ob.map, clusters, stream);
-    } else {
-        const int grid = static_cast<int>(total < st.sm_count ? total : st.sm_count);
-        rc = dispatch(pl.bn, pl.bk, pl.tma, p, oa.map, ob.map, grid, stream);
-    }
+    auto launch = [&](const GemmParams& q) -> int {
+        if (pl.pair) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            int clusters = max_pair_clusters(dev);
+            if (clusters <= 0) return B200_EDEVICE;
+            if (clusters > q.total_work) clusters = q.total_work;
+            return launch_pair(q, oa.map, ob.map, clusters, stream);
+        }
+        const int grid = q.total_work < st.sm_count ? q.total_work : st.sm_count;
+        return dispatch(pl.bn, pl.bk, pl.tma, q, oa.map, ob.map, grid, stream);
+    };
+    int rc = launch(p);
     if (rc) return rc;
+    if (pl.tail_tiles > 0) {
+        GemmParams q = p;
+        q.tile_offset = pl.full_tiles;
+        q.tail_tiles = pl.tail_tiles;
+        q.split_k = pl.tail_split;
+        q.kb_per_split = pl.tail_kb_per_split;
+        q.total_work = pl.tail_tiles * pl.tail_split;
+        rc = launch(q);
+        if (rc) return rc;
+        tail_reduce_kernel<<<pl.tail_tiles * 8, 256, 0, stream>>>(q, pl.pair ? 2 * kBM : kBM, pl.bn);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        rc = static_cast<int>(cudaGetLastError());
+        if (rc) return rc;
+    }
     if (pl.split_k > 1) {
         const int64_t elems = batch * M * N;
         int blocks = static_cast<int>((elems + 255) / 256);
@@ -653,7 +707,7 @@ size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K) {
         st = &tmp;
     }
     Plan pl = make_plan(*st, batch, M, N, K, true, static_cast<size_t>(-1));
-    if (pl.split_k <= 1) return 0;
+    if (pl.split_k <= 1) return pl.tail_bytes;
     return static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float);
 }
 
@@ -791,6 +845,8 @@ int b200_gemm_set_option(const char* name, long value) {
         g_opt.promote_every = value;
     } else if (!std::strcmp(name, "force_ldg")) {
         g_opt.force_ldg = value ? 1 : 0;
+    } else if (!std::strcmp(name, "tail_split")) {
+        g_opt.tail_split = value ? 1 : 0;
     } else if (!std::strcmp(name, "host_pipeline")) {
         g_opt.host_pipeline = value ? 1 : 0;
     } else if (!std::strcmp(name, "pair_mode")) {

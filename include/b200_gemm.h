@@ -111,8 +111,8 @@ int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, i
  * every GPU that loads the library until the process exits.  The call performs no cudaMalloc,
  * cudaFree or other allocating call.
  *
- * Same arguments and arithmetic as b200_gemm_f32; results are identical to it when it is given
- * ample workspace.  Differences:
+ * Same arguments and arithmetic as b200_gemm_f32; results are identical to what that function
+ * returns when it is handed a workspace of the same 4 MiB.  Differences:
  *   - a shape whose split-K plan needs more than 4 MiB of partials is refused with
  *     B200_ENOSPACE (the automatic plan never needs more than about 2.4 MB on a B200; forced
  *     "split_k" / "tile_n" options can);
@@ -145,6 +145,8 @@ uint64_t b200_gemm_launch_count(void);
  *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
  *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path
+ *   "tail_split"    1 (default) = when the last wave of tiles would leave most SMs idle, run its
+ *                   tiles split along K in a second launch (needs workspace), 0 = never
  *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math, 0 = one
  *                   upload, one kernel, one download
  *   "pair_mode"     0 = automatic, 1 = never, 2 = whenever legal: run 256 x 256 tiles on pairs of

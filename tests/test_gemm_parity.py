@@ -221,6 +221,41 @@ def test_pair_and_single_kernels_agree_bitwise(pkg, orc, cuda):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("beta", [0.0, 1.0])
+def test_tail_wave_split(pkg, orc, cuda, beta):
+    """80 pair tiles on 74 clusters: the 6 tiles of the last wave run split four ways along K in a
+    second launch and are reduced in a fixed order.  Exact on integers, deterministic, and equal
+    within tolerance to the unsplit plan."""
+    import torch
+
+    M, N, K = 2560, 2048, 1024
+    ws_bytes = pkg.workspace_bytes(1, M, N, K)
+    assert ws_bytes > 0, "expected the tail-wave plan for this shape"
+    rng = np.random.default_rng(5)
+    a = rng.integers(-4, 5, size=(M, K)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(K, N)).astype(np.float32)
+    c0 = rng.integers(-5, 6, size=(M, N)).astype(np.float32)
+    want = orc.matmul(a, b) + beta * c0
+    A, B = dev(a, cuda), dev(b, cuda)
+    outs = []
+    for _ in range(2):
+        C = dev(c0, cuda)
+        gemm(pkg, cuda, A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, beta=beta, ws_bytes=ws_bytes)
+        outs.append(C.cpu().numpy())
+    assert np.array_equal(outs[0], want) and np.array_equal(outs[0], outs[1])
+    g = orc.Rng(6)
+    ar, br = g.randn((M, K)), g.randn((K, N))
+    Ar, Br = dev(ar, cuda), dev(br, cuda)
+    C1 = torch.empty((M, N), device=cuda)
+    C2 = torch.empty((M, N), device=cuda)
+    gemm(pkg, cuda, Ar, Br, C1, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, ws_bytes=ws_bytes)
+    gemm(pkg, cuda, Ar, Br, C2, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, ws_bytes=0)
+    wantr = orc.matmul(ar, br)
+    assert orc.scaled_error(C1.cpu().numpy(), wantr) <= orc.parity_tolerance(K)
+    # two summation orders of the same fp32 sum: each is within the K-dependent bound of the truth
+    assert orc.scaled_error(C1.cpu().numpy(), C2.cpu().numpy()) <= orc.parity_tolerance(K)
+
+
 def test_golden_pytorch_vectors_forward(pkg, cuda, golden_dir):
     """tests/test_reference.cpp:99-114, abs tolerance 1e-4."""
     z = np.load(golden_dir / "pytorch_matmul.npz")
