@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--no-extras", action="store_true", help="skip 4096^3, e2e and the CPU baseline")
     ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 peak measurement (profiling runs)")
+    ap.add_argument("--suite", default="", choices=["", "engine"],
+                    help="'engine': time every GEMM of the char-LM, CNN and relu-sparse configurations "
+                         "(one JSON line per shape) instead of the large-square benchmark")
     return ap.parse_args()
 
 
@@ -458,8 +461,100 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------
+# engine-sized shapes (configurations 1-4): HBM- or latency-bound, reported per launch
+# ------------------------------------------------------------------------------------------
+ENGINE_SHAPES = [
+    # name, batch, M, N, K, transA, transB, a_batched, b_batched
+    ("cfg1 bench 512^3", 1, 512, 512, 512, 0, 0, 0, 0),
+    ("cfg2 proj fwd 2048x96x96", 1, 2048, 96, 96, 0, 0, 0, 0),
+    ("cfg2 fused-QKV fwd 2048x96x288", 1, 2048, 288, 96, 0, 0, 0, 0),
+    ("cfg2 FF1 fwd 2048x96x384", 1, 2048, 384, 96, 0, 0, 0, 0),
+    ("cfg2 FF2 fwd 2048x384x96", 1, 2048, 96, 384, 0, 0, 0, 0),
+    ("cfg2 LM head fwd 2048x96x121", 1, 2048, 121, 96, 0, 0, 0, 0),
+    ("cfg2 dX=dY.W^T (FF1) NT", 1, 2048, 96, 384, 0, 1, 0, 0),
+    ("cfg2 dW=X^T.dY (FF1) TN", 1, 96, 384, 2048, 1, 0, 0, 0),
+    ("cfg2 scores Q.K^T NT b128", 128, 64, 64, 24, 0, 1, 1, 1),
+    ("cfg2 context P.V b128", 128, 64, 24, 64, 0, 0, 1, 1),
+    ("cfg2 dV=P^T.dO TN b128", 128, 64, 24, 64, 1, 0, 1, 1),
+    ("cfg3 conv1 fwd cols.W^T NT", 1, 50176, 8, 9, 0, 1, 0, 0),
+    ("cfg3 conv1 dW cols^T.dOut TN", 1, 9, 8, 50176, 1, 0, 0, 0),
+    ("cfg3 conv2 fwd NT", 1, 12544, 16, 72, 0, 1, 0, 0),
+    ("cfg3 conv2 dW TN", 1, 72, 16, 12544, 1, 0, 0, 0),
+    ("cfg3 conv2 dCols", 1, 12544, 72, 16, 0, 0, 0, 0),
+    ("cfg3 dense fwd 64x784x10", 1, 64, 10, 784, 0, 0, 0, 0),
+    ("cfg4 relu-sparse 2048^3 NN", 1, 2048, 2048, 2048, 0, 0, 0, 0),
+    ("cfg4 relu-sparse 2048^3 NT", 1, 2048, 2048, 2048, 0, 1, 0, 0),
+    ("cfg4 relu-sparse 2048^3 TN", 1, 2048, 2048, 2048, 1, 0, 0, 0),
+]
+
+
+def run_engine_suite(args):
+    import torch
+
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    pkg.load()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    hbm = json.loads(peaks_file.read_text()).get("hbm_gbs", 6650.0) if peaks_file.exists() else 6650.0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    for name, batch, M, N, K, tA, tB, ab, bb in ENGINE_SHAPES:
+        a_shape = ((batch,) if ab else ()) + ((K, M) if tA else (M, K))
+        b_shape = ((batch,) if bb else ()) + ((N, K) if tB else (K, N))
+        A = torch.randn(a_shape, device=dev, generator=gen)
+        if "relu" in name or "FF2" in name:
+            A = torch.relu(A)
+        B = torch.randn(b_shape, device=dev, generator=gen)
+        C = torch.empty((batch, M, N), device=dev)
+        ws_bytes = pkg.workspace_bytes(batch, M, N, K)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+        def launch():
+            pkg.gemm(A, B, C, batch=batch, M=M, N=N, K=K, transA=bool(tA), transB=bool(tB),
+                     lda=a_shape[-1], ldb=b_shape[-1], ldc=N, strideA=(K * M if ab else 0),
+                     strideB=(K * N if bb else 0), strideC=M * N, workspace=ws, workspace_bytes=ws_bytes)
+
+        for _ in range(5):
+            launch()
+        torch.cuda.synchronize()
+        iters = 50
+        e0.record()
+        for _ in range(iters):
+            launch()
+        e1.record()
+        torch.cuda.synchronize()
+        hot_us = e0.elapsed_time(e1) / iters * 1e3
+        cold = []
+        for _ in range(10):
+            flush.fill_(1)
+            e0.record()
+            launch()
+            e1.record()
+            torch.cuda.synchronize()
+            cold.append(e0.elapsed_time(e1) * 1e3)
+        pkg.status()
+        cold_us = statistics.median(cold)
+        bytes_alg = 4.0 * ((batch if ab else 1) * M * K + (batch if bb else 1) * K * N + batch * M * N)
+        flops = 2.0 * batch * M * N * K
+        print(json.dumps({
+            "shape": name, "batch": batch, "M": M, "N": N, "K": K, "transA": tA, "transB": tB,
+            "us_per_launch_back_to_back": round(hot_us, 2), "us_per_launch_l2_flushed": round(cold_us, 2),
+            "algorithmic_bytes": int(bytes_alg), "useful_tflops_back_to_back": round(flops / hot_us / 1e6, 3),
+            "hbm_gbs_l2_flushed": round(bytes_alg / cold_us / 1e3, 1),
+            "frac_of_measured_hbm": round(bytes_alg / cold_us / 1e3 / hbm, 4),
+            "kernels_per_call": 2 if ws_bytes else 1}), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.suite == "engine":
+        run_engine_suite(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
