@@ -44,6 +44,7 @@ struct Options {
     long pair_mode = 0;  // 0 automatic, 1 never, 2 whenever legal
     long host_pipeline = 1;  // b200_matmul_f32_host: overlap transfers with the math
     long tail_split = 1;     // split the tiles of a mostly-empty last wave along K
+    long group_m = 0;        // tile rows per scheduling band; 0 = automatic
 };
 Options g_opt;
 #ifdef B200_PHASE_PROFILE
@@ -414,7 +415,9 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     p.kblocks = pl.kblocks;
     p.split_k = pl.split_k;
     p.kb_per_split = pl.kb_per_split;
-    p.group_m = 16;
+    // The tiles in flight at one time should cover a near-square patch of C: 74 pair tiles are
+    // 8 x 9, 148 single tiles (128 x 256) are 16 x 9.
+    p.group_m = g_opt.group_m > 0 ? static_cast<int>(g_opt.group_m) : (pl.pair ? 8 : 16);
     p.total_work = static_cast<int>(total);
     p.A = A;
     p.B = B;
@@ -845,6 +848,9 @@ int b200_gemm_set_option(const char* name, long value) {
         g_opt.promote_every = value;
     } else if (!std::strcmp(name, "force_ldg")) {
         g_opt.force_ldg = value ? 1 : 0;
+    } else if (!std::strcmp(name, "group_m")) {
+        if (value < 0 || value > 4096) return B200_EINVAL;
+        g_opt.group_m = value;
     } else if (!std::strcmp(name, "tail_split")) {
         g_opt.tail_split = value ? 1 : 0;
     } else if (!std::strcmp(name, "host_pipeline")) {

@@ -145,6 +145,7 @@ uint64_t b200_gemm_launch_count(void);
  *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
  *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path
+ *   "group_m"       tile rows per scheduling band (0 = automatic: 8 for pair tiles, 16 otherwise)
  *   "tail_split"    1 (default) = when the last wave of tiles would leave most SMs idle, run its
  *                   tiles split along K in a second launch (needs workspace), 0 = never
  *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math, 0 = one
