@@ -323,7 +323,11 @@ def run_b200(args):
         achieved = kfac * value
         line["roofline"] = {
             "bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s",
-            "frac": achieved / sustained, "traffic": None,
+            "frac": achieved / sustained,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this workload
+            # (profiles/gemm_tf32_kernel_pair_16384cubed_dram.md); algorithmic bytes are 3 * n^2 * 4
+            "traffic": 43067955968 if (n == BIG and kfac == 3) else None,
+            "algorithmic_bytes": int(3 * n * n * 4),
             "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per launch "
                     f"(2*M*N*K*{kfac}) / mean launch time by CUDA events; peak = cuBLAS TF32 8192^3 "
                     f"sustained loop measured in this run (of measured); burst {burst:.1f}",
