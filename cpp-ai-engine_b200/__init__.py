@@ -18,6 +18,7 @@ from .lib import (  # noqa: F401
     PRECISION_TF32,
     gemm,
     gemm_colshard,
+    gemm_fused,
     gemm_static_scratch,
     launch_count,
     lib_path,
@@ -28,4 +29,4 @@ from .lib import (  # noqa: F401
     workspace_bytes,
 )
 from . import engine, lib, shard  # noqa: F401
-from .engine import Tensor, matmul, matmul_backward, ops_matmul  # noqa: F401
+from .engine import Tensor, attention_scores, linear, matmul, matmul_backward, ops_matmul  # noqa: F401

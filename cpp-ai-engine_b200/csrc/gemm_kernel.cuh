@@ -72,6 +72,11 @@ struct GemmParams {
     int precision;      // 0 = 3xTF32, 1 = TF32
     int promote_every;  // k-blocks per TMEM accumulation chain
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
+    // fused epilogue: out = act(alpha*acc + beta*out + bias[col] + addend[row][col])
+    const float* bias;    // N values, or null
+    const float* addend;  // M x N (ld_addend), shared by every batch element, or null
+    long long ld_addend;
+    int relu;
     int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
     int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
     int* status;
@@ -166,6 +171,22 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 #define B200_PROF_DECL
 #define B200_PROF_FLUSH(cond)
 #endif
+
+// The fused part of the epilogue, in the order the reference applies its separate operations
+// to a product: bias broadcast add (src/nn.cpp:120-122, src/conv.cpp:323), additive mask
+// (src/transformer.cpp:296); then the accumulation into an existing output; ReLU last
+// (src/transformer.cpp:413).
+__device__ __forceinline__ float add_bias_mask(const GemmParams& p, float v, int row, int col) {
+    if (p.bias) v += __ldg(p.bias + col);
+    if (p.addend) v += __ldg(p.addend + (long long)row * p.ld_addend + col);
+    return v;
+}
+__device__ __forceinline__ float finish_output(const GemmParams& p, float scaled, float old, int row,
+                                               int col) {
+    float v = add_bias_mask(p, scaled, row, col);
+    if (p.beta != 0.f) v += p.beta * old;
+    return p.relu ? fmaxf(v, 0.0f) : v;
+}
 
 // Loads a ROWS x 32 tile of one operand with plain global loads, splits it and stores the
 // head / tail tiles in the K-major 128-byte-swizzled layout.  `k_contig`: k is the contiguous
@@ -619,6 +640,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const long long ld_out = compact ? (long long)BN : split_out ? (long long)p.N : p.ldc;
                 const bool vec = compact ? true : split_out ? ((p.N & 3) == 0) : (p.c_vec_ok != 0);
                 const int n_out = split_out ? 1 : p.n_dest;
+                const bool fuse = !split_out && (p.bias != nullptr || p.addend != nullptr);
+                const bool relu = !split_out && p.relu != 0;
                 // compact: element (row, col) of tail tile t lives at
                 //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
@@ -640,7 +663,10 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     __syncwarp();
                     const int col = col_base + g * 32 + chunk * 4;
                     if (chunk < kChunks && col < p.N) {
-#pragma unroll
+                        // Not unrolled on purpose: 32 copies of the store path (4 column groups x
+                        // 8 row groups) made the kernel 20 % slower at 4096^3 — the k-loop's
+                        // code no longer stayed in the instruction cache.
+#pragma unroll 1
                         for (int it = 0; it < 8; ++it) {
                             const int rr = it * 4 + sub_row;
                             const int row = row_base + rr;
@@ -650,6 +676,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                             v.y *= alpha;
                             v.z *= alpha;
                             v.w *= alpha;
+                            if (fuse) {  // bias / mask do not depend on the destination
+                                if (col + 0 < p.N) v.x = add_bias_mask(p, v.x, row, col + 0);
+                                if (col + 1 < p.N) v.y = add_bias_mask(p, v.y, row, col + 1);
+                                if (col + 2 < p.N) v.z = add_bias_mask(p, v.z, row, col + 2);
+                                if (col + 3 < p.N) v.w = add_bias_mask(p, v.w, row, col + 3);
+                            }
                             const long long off = base_off + (long long)row * ld_out + col;
                             for (int dd = 0; dd < n_out; ++dd) {
                                 float* dst = (split_out ? p.partial : p.dest[dd]) + off;
@@ -662,6 +694,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                                         o.z += beta * old.z;
                                         o.w += beta * old.w;
                                     }
+                                    if (relu) {
+                                        o.x = fmaxf(o.x, 0.f);
+                                        o.y = fmaxf(o.y, 0.f);
+                                        o.z = fmaxf(o.z, 0.f);
+                                        o.w = fmaxf(o.w, 0.f);
+                                    }
                                     *reinterpret_cast<float4*>(dst) = o;
                                 } else {
                                     const float e4[4] = {v.x, v.y, v.z, v.w};
@@ -670,6 +708,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                                         if (col + e < p.N) {
                                             float o = e4[e];
                                             if (beta != 0.f) o += beta * dst[e];
+                                            if (relu) o = fmaxf(o, 0.f);
                                             dst[e] = o;
                                         }
                                     }
@@ -704,9 +743,10 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
 
 // C = alpha * sum_s partial[s] + beta * C, splits added in ascending order so the result does
 // not depend on scheduling.  One thread per output element.
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ C,
-                                     int split, long long batch, long long M, long long N,
-                                     long long ldc, long long strideC, float alpha, float beta) {
+__global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict__ partial,
+                                     float* __restrict__ C, int split, long long batch, long long M,
+                                     long long N, long long ldc, long long strideC, float alpha,
+                                     float beta) {
     const long long total = batch * M * N;
     const long long step = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
@@ -716,9 +756,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* _
         const long long r = (i - b * M * N) / N;
         const long long c = i - b * M * N - r * N;
         float* out = C + b * strideC + r * ldc + c;
-        float o = alpha * s;
-        if (beta != 0.f) o += beta * *out;
-        *out = o;
+        *out = finish_output(p, alpha * s, beta != 0.f ? *out : 0.f, static_cast<int>(r),
+                             static_cast<int>(c));
     }
 }
 
@@ -752,9 +791,7 @@ __global__ void tail_reduce_kernel(const GemmParams p, int tile_rows, int bn) {
         const float e4[4] = {s.x, s.y, s.z, s.w};
         for (int e = 0; e < 4; ++e) {
             if (col + e < p.N) {
-                float o = p.alpha * e4[e];
-                if (p.beta != 0.f) o += p.beta * out[e];
-                out[e] = o;
+                out[e] = finish_output(p, p.alpha * e4[e], p.beta != 0.f ? out[e] : 0.f, row, col + e);
             }
         }
     }

@@ -365,7 +365,12 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
               int64_t batch, int64_t M, int64_t N, int64_t K, int transA, int transB, int64_t lda,
               int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB, int64_t strideC,
               float alpha, float beta, int precision, void* workspace, size_t workspace_bytes,
-              cudaStream_t stream) {
+              cudaStream_t stream, const b200_epilogue* ep = nullptr) {
+    if (ep != nullptr) {
+        if (ep->addend != nullptr && ep->ld_addend < N) return B200_EINVAL;
+        if (ep->relu != 0 && ep->relu != 1) return B200_EINVAL;
+        if (K == 0 && (ep->bias || ep->addend || ep->relu)) return B200_EINVAL;  // nothing to fuse into
+    }
     if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
     if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
     if (n_dest < 1 || n_dest > kMaxDest || dest == nullptr) return B200_EINVAL;
@@ -437,6 +442,12 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     p.promote_every = g_opt.promote_every >= 1 ? static_cast<int>(g_opt.promote_every) : 1;
     p.partial = static_cast<float*>(workspace);
     p.status = st.status;
+    if (ep != nullptr) {
+        p.bias = ep->bias;
+        p.addend = ep->addend;
+        p.ld_addend = ep->ld_addend;
+        p.relu = ep->relu;
+    }
 #ifdef B200_PHASE_PROFILE
     p.prof = g_prof;
 #endif
@@ -514,7 +525,7 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         const int64_t elems = batch * M * N;
         int blocks = static_cast<int>((elems + 255) / 256);
         if (blocks > st.sm_count * 8) blocks = st.sm_count * 8;
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(workspace), C,
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p, static_cast<const float*>(workspace), C,
                                                          pl.split_k, batch, M, N, ldc, strideC,
                                                          alpha, beta);
         g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -699,6 +710,22 @@ int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64
     return gemm_impl(*st, A, B, dest, 1, batch, M, N, K, transA, transB, lda, ldb, ldc, strideA,
                      strideB, strideC, alpha, beta, precision, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_f32_fused(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+                        int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
+                        int64_t strideA, int64_t strideB, int64_t strideC, float alpha, float beta,
+                        int precision, const b200_epilogue* epilogue, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    float* dest[1] = {C};
+    if (C == nullptr) return B200_EINVAL;
+    if (batch == 1 && strideC == 0) strideC = M * ldc;
+    return gemm_impl(*st, A, B, dest, 1, batch, M, N, K, transA, transB, lda, ldb, ldc, strideA,
+                     strideB, strideC, alpha, beta, precision, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), epilogue);
 }
 
 size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K) {

@@ -147,6 +147,57 @@ def matmul_backward(a, b, grad_out, *, precision: int = _lib.PRECISION_3XTF32, s
     return dA, dB
 
 
+def linear(x, weight, bias=None, *, relu: bool = False, precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """``Linear::forward`` (src/nn.cpp:101-130): leading axes flattened, ``flat.matmul(weight)`` with the
+    weight stored (in, out), bias broadcast over rows — and, fused into the same kernel's store, the
+    bias add and an optional ReLU (the feed-forward ``ff1(x).relu()``, src/transformer.cpp:413)."""
+    import torch
+
+    _check_operand(x, "x")
+    _check_operand(weight, "weight")
+    if weight.dim() != 2 or x.shape[-1] != weight.shape[0]:
+        raise ValueError(f"Linear expects (..., {weight.shape[0]}) inputs, got {tuple(x.shape)}.")
+    if bias is not None:
+        _check_operand(bias, "bias")
+        if list(bias.shape) != [weight.shape[1]]:
+            raise ValueError("bias must have one value per output feature")
+    rows = x.numel() // x.shape[-1]
+    K, N = weight.shape
+    out = torch.empty(list(x.shape[:-1]) + [N], dtype=torch.float32, device=x.device)
+    if out.numel() == 0:
+        return out
+    ws_bytes = _lib.workspace_bytes(1, rows, N, K)
+    ws, ws_bytes = _workspace(x.device, ws_bytes)
+    _lib.gemm_fused(x, weight, out, batch=1, M=rows, N=N, K=K, lda=K, ldb=N, ldc=N, bias=bias, relu=relu,
+                    precision=precision, workspace=ws, workspace_bytes=ws_bytes, stream=stream)
+    return out
+
+
+def attention_scores(q, k, scale: float, mask=None, *, precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """``scores = q.matmul(k.transpose()) * scale + mask`` (src/transformer.cpp:292-297) as ONE kernel:
+    K is read as stored (transB), the scale is the product's alpha and the additive mask, shared by
+    every head, is added in the store.  q, k: (..., S, d); mask: (S, S) or None."""
+    import torch
+
+    _check_operand(q, "q")
+    _check_operand(k, "k")
+    if q.dim() < 2 or list(q.shape[:-2]) != list(k.shape[:-2]) or q.shape[-1] != k.shape[-1]:
+        raise ValueError(f"attention needs matching batch axes and head size: {tuple(q.shape)} and {tuple(k.shape)}.")
+    S, d, Sk = q.shape[-2], q.shape[-1], k.shape[-2]
+    batch = q.numel() // (S * d) if S * d else 0
+    if mask is not None:
+        _check_operand(mask, "mask")
+        if list(mask.shape) != [S, Sk]:
+            raise ValueError("mask must be (S_q, S_k)")
+    out = torch.empty(list(q.shape[:-2]) + [S, Sk], dtype=torch.float32, device=q.device)
+    if out.numel() == 0:
+        return out
+    _lib.gemm_fused(q, k, out, batch=batch, M=S, N=Sk, K=d, transB=True, lda=d, ldb=d, ldc=Sk,
+                    strideA=S * d, strideB=Sk * d, strideC=S * Sk, alpha=float(scale), addend=mask,
+                    ld_addend=Sk, precision=precision, stream=stream)
+    return out
+
+
 class Tensor:
     """The slice of ``engine::Tensor`` the matrix-product path needs: a value, an optional
     gradient, ``matmul`` and ``backward`` (include/engine/tensor.hpp:157-198)."""

@@ -20,6 +20,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "b200_gemm_f32",
+    "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
     "b200_matmul_f32",
     "b200_matmul_f32_host",
@@ -30,6 +31,12 @@ EXPORTS = (
     "b200_gemm_set_option",
     "b200_gemm_strerror",
 )
+
+
+class Epilogue(ctypes.Structure):
+    """``b200_epilogue``: bias[N], addend[M x N] (shared across the batch), relu flag."""
+    _fields_ = [("bias", ctypes.c_void_p), ("addend", ctypes.c_void_p), ("ld_addend", ctypes.c_int64),
+                ("relu", ctypes.c_int)]
 
 
 class B200Error(RuntimeError):
@@ -58,6 +65,10 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_f32.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
                                   c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f, c_int,
                                   c_vp, c_sz, c_vp]
+    lib.b200_gemm_f32_fused.restype = c_int
+    lib.b200_gemm_f32_fused.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
+                                        c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f, c_int,
+                                        ctypes.POINTER(Epilogue), c_vp, c_sz, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
     lib.b200_gemm_f32_workspace.argtypes = [c_i64, c_i64, c_i64, c_i64]
     lib.b200_matmul_f32.restype = c_int
@@ -130,6 +141,19 @@ def gemm_static_scratch(A, B, C, *, batch: int, M: int, N: int, K: int, transA: 
                                              alpha, beta, precision, _ptr(device_status),
                                              _stream_ptr(stream))
     _check(rc, "b200_gemm_f32_static_scratch")
+
+
+def gemm_fused(A, B, C, *, batch: int, M: int, N: int, K: int, transA: bool = False, transB: bool = False,
+               lda: int, ldb: int, ldc: int, strideA: int = 0, strideB: int = 0, strideC: int = 0,
+               alpha: float = 1.0, beta: float = 0.0, precision: int = PRECISION_3XTF32, bias=None,
+               addend=None, ld_addend: int = 0, relu: bool = False, workspace=None, workspace_bytes: int = 0,
+               stream=None) -> None:
+    """``C = relu?(alpha * op(A) @ op(B) + bias[col] + addend[row, col] + beta * C)`` in one kernel."""
+    ep = Epilogue(_ptr(bias) or None, _ptr(addend) or None, ld_addend or N, int(relu))
+    rc = load().b200_gemm_f32_fused(_ptr(A), _ptr(B), _ptr(C), batch, M, N, K, int(transA), int(transB),
+                                    lda, ldb, ldc, strideA, strideB, strideC, alpha, beta, precision,
+                                    ctypes.byref(ep), _ptr(workspace), workspace_bytes, _stream_ptr(stream))
+    _check(rc, "b200_gemm_f32_fused")
 
 
 def workspace_bytes(batch: int, M: int, N: int, K: int) -> int:

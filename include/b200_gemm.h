@@ -63,6 +63,29 @@ int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64
                   int64_t strideA, int64_t strideB, int64_t strideC, float alpha, float beta,
                   int precision, void* workspace, size_t workspace_bytes, void* stream);
 
+/* What the reference does in separate element-wise kernels right after a product, folded into
+ * the product's own store (no reference counterpart as one call; the operations are
+ * Linear's and Conv2d's bias broadcast add, src/nn.cpp:120-122 and src/conv.cpp:323; attention's
+ * `* scale` then `+ mask`, src/transformer.cpp:292-297; the feed-forward ReLU,
+ * src/transformer.cpp:413).  Applied in this order, each an fp32 operation on the fp32 result,
+ * exactly as the separate kernels would:
+ *     out = relu?( alpha * (op(A) x op(B)) + bias[col] + addend[row][col] + beta * out )
+ * bias: N device floats or NULL.  addend: an M x N device matrix (leading dimension ld_addend >= N)
+ * shared by every batch element, or NULL.  relu: 0 or 1. */
+typedef struct b200_epilogue {
+    const float* bias;
+    const float* addend;
+    int64_t ld_addend;
+    int relu;
+} b200_epilogue;
+
+/* b200_gemm_f32 with the fused epilogue above (epilogue == NULL behaves like b200_gemm_f32). */
+int b200_gemm_f32_fused(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+                        int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
+                        int64_t strideA, int64_t strideB, int64_t strideC, float alpha, float beta,
+                        int precision, const b200_epilogue* epilogue, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials
  * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */
