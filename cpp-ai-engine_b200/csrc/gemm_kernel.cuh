@@ -77,6 +77,9 @@ struct GemmParams {
     const float* addend;  // M x N (ld_addend), shared by every batch element, or null
     long long ld_addend;
     int relu;
+    // implicit-GEMM convolution (conv kernels only): A is gathered from an NCHW input instead of a
+    // stored column matrix, and the output is stored NCHW
+    int cv_c, cv_h, cv_w, cv_kh, cv_kw, cv_stride, cv_pad, cv_oh, cv_ow;
     int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
     int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
     int* status;
@@ -259,7 +262,61 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
     }
 }
 
-template <int BN, int BK, bool kTma, bool kPair = false>
+// Implicit im2col: the 128 x 32 A tile of a convolution, gathered straight from the NCHW input
+// (what nn::im2col would have written to row m = (n, oh, ow), column k = (c, kh, kw),
+// src/conv.cpp:61-150; zero outside the padded border), split and stored like any A tile.
+// Consecutive threads take consecutive output pixels, which are consecutive input addresses
+// for stride 1.
+__device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int row0, int k0,
+                                                        uint8_t* hi, uint8_t* lo, bool want_lo,
+                                                        int wtid) {
+    constexpr int kUnits = kBM * 8;
+    constexpr int kPer = kUnits / kWorkerThreads;
+    const int ohw = p.cv_oh * p.cv_ow;
+    const int khw = p.cv_kh * p.cv_kw;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit % kBM, c = unit / kBM;
+        const int gr = row0 + r;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (gr < p.M) {
+            const int img = gr / ohw, pix = gr - img * ohw;
+            const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
+            const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int gk = k0 + c * 4 + e;
+                if (gk < p.K) {
+                    const int ci = gk / khw, rem = gk - ci * khw;
+                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    const int ih = ih0 + kh, iw = iw0 + kw;
+                    if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w) {
+                        x4[e] = __ldg(p.A + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
+                    }
+                }
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit % kBM, c = unit / kBM;
+        const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
+                             (uint32_t)((c ^ (r & 7)) << 4);
+        float4 h, l;
+        tf32_split(v[u].x, h.x, l.x);
+        tf32_split(v[u].y, h.y, l.y);
+        tf32_split(v[u].z, h.z, l.z);
+        tf32_split(v[u].w, h.w, l.w);
+        *reinterpret_cast<float4*>(hi + off) = h;
+        if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
+    }
+}
+
+template <int BN, int BK, bool kTma, bool kPair = false, bool kConv = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                  const __grid_constant__ CUtensorMap mapB) {
@@ -270,6 +327,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     constexpr int kArrivals = kPair ? 2 * kWorkerWarps : kWorkerWarps;
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
     static_assert(!kPair || kTma, "pair mode loads with TMA");
+    static_assert(!kConv || !kTma, "the convolution gathers its A operand in registers");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -592,8 +650,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const int k0 = (wk.kb0 + i) * BK;
                     const float* a_base = p.A + (long long)wk.b * p.strideA;
                     const float* b_base = p.B + (long long)wk.b * p.strideB;
-                    ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
-                                         p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
+                    if constexpr (kConv) {
+                        conv_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                    } else {
+                        ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
+                                             p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
+                    }
                     ldg_split_store<BN>(b_base, p.ldb, p.transB != 0, p.b_vec_ok != 0, wk.nt * BN,
                                         p.N, k0, p.K, stage + Cfg::kABytes,
                                         stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
@@ -627,7 +689,29 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores rows:
             // one instruction writes four full 128-byte row segments — what HBM and, for the
             // peers' copies of C, NVLink want.
-            {
+            if constexpr (kConv) {
+                // The product's row m = (n, oh, ow) and column oc go to y[n][oc][oh][ow]: for one
+                // column, the 32 rows a warp holds are 32 consecutive floats, so the threads store
+                // their own registers directly and the (N, spatial, C) -> (N, C, H, W) permute of
+                // Conv2d::forward (src/conv.cpp:335-337) never happens as a separate pass.
+                const int row = wk.mt * kBM + quarter * 32 + lane;
+                const int col_base = wk.nt * BN + half * kCols;
+                if (row < p.M) {
+                    const int ohw = p.cv_oh * p.cv_ow;
+                    const int img = row / ohw, pix = row - img * ohw;
+                    float* ybase = p.dest[0] + (long long)img * p.N * ohw + pix;
+#pragma unroll
+                    for (int j = 0; j < kCols; ++j) {
+                        const int col = col_base + j;
+                        if (col < p.N) {
+                            float o = p.alpha * acc[j];
+                            if (p.bias) o += __ldg(p.bias + col);
+                            if (p.relu) o = fmaxf(o, 0.f);
+                            ybase[(long long)col * ohw] = o;
+                        }
+                    }
+                }
+            } else {
                 float4* tile = reinterpret_cast<float4*>(smem + kStages * Cfg::kStageBytes) + wid * 256;
                 const int row_base = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32;
                 const int col_base = wk.nt * BN + half * kCols;

@@ -230,6 +230,26 @@ int launch_pair(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& m
     return static_cast<int>(e);
 }
 
+// Convolution kernels: register-staged loader with the implicit im2col gather.
+template <int BN>
+int launch_conv_cfg(const GemmParams& p, int grid, cudaStream_t stream) {
+    using Cfg = TileCfg<BN, 32>;
+    static bool attr_set[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kernel = gemm_tf32_kernel<BN, 32, false, false, true>;
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(Cfg::kSmemBytes));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_set[dev] = true;
+    }
+    CUtensorMap unused{};
+    kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p, unused, unused);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return static_cast<int>(cudaGetLastError());
+}
+
 int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& ma,
              const CUtensorMap& mb, int grid, cudaStream_t stream) {
 #define B200_CASE(BN_)                                                                     \
@@ -793,6 +813,79 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
         return static_cast<int>(e);
     if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
     return B200_OK;
+}
+
+int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bias, float* y,
+                            int64_t n, int64_t c, int64_t h, int64_t w, int64_t out_c, int64_t kh,
+                            int64_t kw, int64_t stride, int64_t pad, int relu, int precision,
+                            void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (n < 0 || c <= 0 || out_c <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0) return B200_EINVAL;
+    if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (h + 2 * pad < kh || w + 2 * pad < kw) return B200_EINVAL;  // empty output
+    const int64_t oh = (h + 2 * pad - kh) / stride + 1, ow = (w + 2 * pad - kw) / stride + 1;
+    const int64_t M = n * oh * ow, K = c * kh * kw, N = out_c;
+    if (M == 0) return B200_OK;
+    if (x == nullptr || weight == nullptr || y == nullptr) return B200_EINVAL;
+    if (M > 0x7fffffffll || K > 0x7fffffffll || n * c * h * w > 0x7fffffffffffll) return B200_ERANGE;
+    // narrowest tile that covers the output channels, as for any narrow product
+    int bn = 32;
+    for (int cand : {256, 128, 64, 32}) {
+        if (cand > 32 && N <= cand / 2) continue;
+        const int64_t tiles = ceil_div(M, kBM) * static_cast<int64_t>(ceil_div(N, cand));
+        bn = cand;
+        if (tiles >= st->sm_count) break;
+    }
+    GemmParams p{};
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.K = static_cast<int>(K);
+    p.batch = 1;
+    p.tiles_m = ceil_div(M, kBM);
+    p.tiles_n = ceil_div(N, bn);
+    p.kblocks = ceil_div(K, 32);
+    p.split_k = 1;
+    p.kb_per_split = p.kblocks;
+    p.group_m = 16;
+    p.total_work = p.tiles_m * p.tiles_n;
+    p.A = x;
+    p.B = weight;  // (out_c, K) row-major: the transposed-B form, no transpose is built
+    p.dest[0] = y;
+    p.n_dest = 1;
+    p.ldb = K;
+    p.ldc = N;
+    p.transB = 1;
+    p.alpha = 1.0f;
+    p.precision = precision;
+    p.promote_every = g_opt.promote_every >= 1 ? static_cast<int>(g_opt.promote_every) : 1;
+    p.status = st->status;
+    p.bias = bias;
+    p.relu = relu ? 1 : 0;
+    p.b_vec_ok = ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0 && (K & 3) == 0) ? 1 : 0;
+    p.a_lbo = p.b_lbo = 16;
+    p.a_sbo = p.b_sbo = 1024;
+    p.a_kstep = p.b_kstep = 32;
+    p.a_layout = p.b_layout = kLayoutSw128;
+    p.idesc = make_idesc_tf32(kBM, bn, 0, 0);
+    p.cv_c = static_cast<int>(c);
+    p.cv_h = static_cast<int>(h);
+    p.cv_w = static_cast<int>(w);
+    p.cv_kh = static_cast<int>(kh);
+    p.cv_kw = static_cast<int>(kw);
+    p.cv_stride = static_cast<int>(stride);
+    p.cv_pad = static_cast<int>(pad);
+    p.cv_oh = static_cast<int>(oh);
+    p.cv_ow = static_cast<int>(ow);
+    const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (bn) {
+        case 32: return launch_conv_cfg<32>(p, grid, s);
+        case 64: return launch_conv_cfg<64>(p, grid, s);
+        case 128: return launch_conv_cfg<128>(p, grid, s);
+        default: return launch_conv_cfg<256>(p, grid, s);
+    }
 }
 
 int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,

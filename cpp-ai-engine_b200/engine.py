@@ -198,6 +198,37 @@ def attention_scores(q, k, scale: float, mask=None, *, precision: int = _lib.PRE
     return out
 
 
+def conv2d(x, weight, bias=None, *, stride: int = 1, padding: int = 0, relu: bool = False,
+           precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """``Conv2d::forward`` (src/conv.cpp:280-338): x (N, C, H, W), weight (outC, C, kH, kW), optional bias
+    (outC,) -> (N, outC, oH, oW).  One implicit-GEMM kernel instead of im2col + product + bias + permute."""
+    import torch
+
+    _check_operand(x, "x")
+    _check_operand(weight, "weight")
+    if x.dim() != 4:
+        raise ValueError(f"Conv2d expects a 4D volume (N, C, H, W), received {tuple(x.shape)}.")
+    if weight.dim() != 4 or x.shape[1] != weight.shape[1]:
+        raise ValueError(f"Conv2d with in_channels={weight.shape[1] if weight.dim() == 4 else '?'} "
+                         f"received an input {tuple(x.shape)}.")
+    if stride < 1 or padding < 0:
+        raise ValueError("Conv2d requires a stride greater than zero and a non-negative padding.")
+    n, c, h, w = x.shape
+    out_c, _, kh, kw = weight.shape
+    if bias is not None:
+        _check_operand(bias, "bias")
+        if list(bias.shape) != [out_c]:
+            raise ValueError("bias must have one value per output channel")
+    if h + 2 * padding < kh or w + 2 * padding < kw:
+        raise ValueError("the window does not fit the padded input")
+    oh, ow = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
+    y = torch.empty((n, out_c, oh, ow), dtype=torch.float32, device=x.device)
+    if y.numel():
+        _lib.conv2d_forward(x, weight, bias, y, n=n, c=c, h=h, w=w, out_c=out_c, kh=kh, kw=kw, stride=stride,
+                            pad=padding, relu=relu, precision=precision, stream=stream)
+    return y
+
+
 class Tensor:
     """The slice of ``engine::Tensor`` the matrix-product path needs: a value, an optional
     gradient, ``matmul`` and ``backward`` (include/engine/tensor.hpp:157-198)."""

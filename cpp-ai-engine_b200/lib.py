@@ -20,6 +20,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "b200_gemm_f32",
+    "b200_conv2d_forward_f32",
     "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
     "b200_matmul_f32",
@@ -69,6 +70,8 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_f32_fused.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
                                         c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f, c_int,
                                         ctypes.POINTER(Epilogue), c_vp, c_sz, c_vp]
+    lib.b200_conv2d_forward_f32.restype = c_int
+    lib.b200_conv2d_forward_f32.argtypes = [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 9 + [c_int, c_int, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
     lib.b200_gemm_f32_workspace.argtypes = [c_i64, c_i64, c_i64, c_i64]
     lib.b200_matmul_f32.restype = c_int
@@ -154,6 +157,15 @@ def gemm_fused(A, B, C, *, batch: int, M: int, N: int, K: int, transA: bool = Fa
                                     lda, ldb, ldc, strideA, strideB, strideC, alpha, beta, precision,
                                     ctypes.byref(ep), _ptr(workspace), workspace_bytes, _stream_ptr(stream))
     _check(rc, "b200_gemm_f32_fused")
+
+
+def conv2d_forward(x, weight, bias, y, *, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int,
+                   stride: int = 1, pad: int = 0, relu: bool = False, precision: int = PRECISION_3XTF32,
+                   stream=None) -> None:
+    """``y = conv2d(x, weight) + bias`` (NCHW) as one implicit-GEMM kernel."""
+    rc = load().b200_conv2d_forward_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), n, c, h, w, out_c, kh, kw,
+                                        stride, pad, int(relu), precision, _stream_ptr(stream))
+    _check(rc, "b200_conv2d_forward_f32")
 
 
 def workspace_bytes(batch: int, M: int, N: int, K: int) -> int:

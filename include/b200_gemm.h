@@ -86,6 +86,19 @@ int b200_gemm_f32_fused(const float* A, const float* B, float* C, int64_t batch,
                         int precision, const b200_epilogue* epilogue, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Conv2d::forward as ONE kernel (src/conv.cpp:280-338 builds it from im2col, a product against
+ * the transposed (out_c, K) weight view, a bias broadcast add and a (N, spatial, C) -> (N, C, H, W)
+ * permute; src/cuda/kernels.cu:394-426 is the reference's im2col_gather kernel).  Implicit GEMM:
+ * the column matrix is never written — the A tiles are gathered from x while they are loaded —
+ * the weight is read as stored, and the store writes y in NCHW order with the bias (and an
+ * optional ReLU) applied.
+ * x: (n, c, h, w); weight: (out_c, c, kh, kw); bias: out_c values or NULL;
+ * y: (n, out_c, oh, ow) with oh = (h + 2*pad - kh) / stride + 1, likewise ow.  All row-major. */
+int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bias, float* y,
+                            int64_t n, int64_t c, int64_t h, int64_t w, int64_t out_c, int64_t kh,
+                            int64_t kw, int64_t stride, int64_t pad, int relu, int precision,
+                            void* stream);
+
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials
  * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */

@@ -7,6 +7,7 @@ Outputs (small, committed):
   pytorch_matmul.npz / .bin   the reference's own PyTorch golden vectors for its matrix product and
                        its gradients (tests/fixtures/matmul*.bin, consumed by
                        tests/test_reference.cpp:99-114), re-encoded as npz.
+  pytorch_conv2d.npz   the reference's PyTorch golden vectors for Conv2d forward (tests/fixtures/conv2d_*.bin).
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
   reference_runs.npz   outputs of the UNMODIFIED reference engine (oracle/_ref) on seeded
                        inputs: its random streams, and per configuration a SHA-256 of the full
@@ -143,6 +144,15 @@ def main() -> None:
             packed[f"{name}/{key}"] = val
     np.savez(HERE / "pytorch_matmul.npz", **packed)
     write_container(HERE / "pytorch_matmul.bin", packed)  # same vectors for the C++ host tests
+
+    # 1b. the reference's PyTorch golden vectors for Conv2d (tests/fixtures/conv2d_*.bin,
+    #     consumed by tests/test_reference.cpp:216-251): inputs, parameters and outputs
+    conv = {}
+    for name in ["conv2d_pad1", "conv2d_stride2"]:
+        fx = read_fixture(ref_dir / "tests" / "fixtures" / f"{name}.bin")
+        for key in ("input", "weight", "bias", "output"):
+            conv[f"{name}/{key}"] = fx[key]
+    np.savez(HERE / "pytorch_conv2d.npz", **conv)
 
     # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
     known = [
