@@ -493,6 +493,13 @@ ENGINE_SHAPES = [
 ]
 
 
+CONV_SHAPES = [
+    # name, n, c, h, w, out_c, k, stride, pad
+    ("cfg3 conv1 layer, implicit GEMM (64,1,28,28)->8", 64, 1, 28, 28, 8, 3, 1, 1),
+    ("cfg3 conv2 layer, implicit GEMM (64,8,14,14)->16", 64, 8, 14, 14, 16, 3, 1, 1),
+]
+
+
 def run_engine_suite(args):
     import torch
 
@@ -552,6 +559,25 @@ def run_engine_suite(args):
             "hbm_gbs_l2_flushed": round(bytes_alg / cold_us / 1e3, 1),
             "frac_of_measured_hbm": round(bytes_alg / cold_us / 1e3 / hbm, 4),
             "kernels_per_call": 2 if ws_bytes else 1}), flush=True)
+    # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel
+    for name, n, c, h, w, out_c, k, stride, pad in CONV_SHAPES:
+        x = torch.rand((n, c, h, w), device=dev, generator=gen)
+        wt = torch.randn((out_c, c, k, k), device=dev, generator=gen)
+        b = torch.randn((out_c,), device=dev, generator=gen)
+        for _ in range(5):
+            y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(50):
+            y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
+        e1.record()
+        torch.cuda.synchronize()
+        hot_us = e0.elapsed_time(e1) / 50 * 1e3
+        pkg.status()
+        bytes_alg = 4.0 * (x.numel() + wt.numel() + b.numel() + y.numel())
+        print(json.dumps({"shape": name, "us_per_launch_back_to_back": round(hot_us, 2),
+                          "algorithmic_bytes": int(bytes_alg), "kernels_per_call": 1,
+                          "note": "includes the output allocation by the Python wrapper"}), flush=True)
 
 
 def main():
