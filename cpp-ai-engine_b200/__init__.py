@@ -14,6 +14,7 @@ from __future__ import annotations
 from . import build as _build  # noqa: F401
 from .lib import (  # noqa: F401
     B200Error,
+    attention_forward,
     conv2d_forward,
     PRECISION_3XTF32,
     PRECISION_TF32,
@@ -30,4 +31,4 @@ from .lib import (  # noqa: F401
     workspace_bytes,
 )
 from . import engine, lib, shard  # noqa: F401
-from .engine import Tensor, attention_scores, conv2d, linear, matmul, matmul_backward, ops_matmul  # noqa: F401
+from .engine import Tensor, attention_scores, conv2d, linear, scaled_dot_product_attention, matmul, matmul_backward, ops_matmul  # noqa: F401

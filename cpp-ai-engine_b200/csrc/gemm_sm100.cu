@@ -2,8 +2,10 @@
 // TMA tensor-map encoding, launches, and the extern "C" surface declared in
 // include/b200_gemm.h.  No CPU fallback exists: a shape the kernels cannot run is an error.
 #include "../../include/b200_gemm.h"
+#include "attention_kernel.cuh"
 #include "gemm_kernel.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -886,6 +888,55 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
         case 128: return launch_conv_cfg<128>(p, grid, s);
         default: return launch_conv_cfg<256>(p, grid, s);
     }
+}
+
+int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
+                       float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                       float scale, int precision, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (batch < 0 || s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
+    if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (s_q > 128 || s_k > kAttnMaxSk || d_k > kAttnMaxD || d_v > kAttnMaxD) return B200_ERANGE;
+    if (batch == 0) return B200_OK;
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return B200_EINVAL;
+    if (batch > 0x7fffffffll) return B200_ERANGE;
+    AttnParams p{};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.mask = mask;
+    p.out = out;
+    p.weights = weights;
+    p.batch = static_cast<int>(batch);
+    p.s_q = static_cast<int>(s_q);
+    p.s_k = static_cast<int>(s_k);
+    p.d_k = static_cast<int>(d_k);
+    p.d_v = static_cast<int>(d_v);
+    p.sk_pad = static_cast<int>((s_k + 31) / 32 * 32);
+    p.dk_pad = static_cast<int>((d_k + 31) / 32 * 32);
+    p.dv_pad = static_cast<int>((d_v + 15) / 16 * 16);
+    p.scale = scale;
+    p.precision = precision;
+    p.status = st->status;
+    const uint32_t q_bytes = 128u * p.dk_pad * 4u, k_bytes = static_cast<uint32_t>(p.sk_pad) * p.dk_pad * 4u;
+    const uint32_t p_bytes = 128u * p.sk_pad * 4u, v_bytes = static_cast<uint32_t>(p.dv_pad) * p.sk_pad * 4u;
+    const uint32_t region1 = std::max(2 * (q_bytes + k_bytes), 2 * p_bytes);
+    const uint32_t smem = region1 + 2 * v_bytes + 1024;
+    static uint32_t attr_bytes[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > attr_bytes[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_bytes[dev] = smem;
+    }
+    const int grid = static_cast<int>(std::min<int64_t>(batch, 2 * st->sm_count));
+    attention_fwd_kernel<<<grid, kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return static_cast<int>(cudaGetLastError());
 }
 
 int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,

@@ -198,6 +198,41 @@ def attention_scores(q, k, scale: float, mask=None, *, precision: int = _lib.PRE
     return out
 
 
+def scaled_dot_product_attention(query, key, value, mask=None, *, return_weights: bool = False,
+                                 precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """``scaled_dot_product_attention`` (src/transformer.cpp:279-304): softmax(Q K^T / sqrt(d_k) + mask) V
+    over the leading (batch, head) axes, fused into one kernel; the (.., S, S) scores never reach global
+    memory.  Returns ``out`` or ``(out, attention_weights)``."""
+    import math
+
+    import torch
+
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        _check_operand(t, name)
+        if t.dim() < 2:
+            raise ValueError("Attention needs at least 2 dimensions (seq, d_k).")
+    d_k = query.shape[-1]
+    if key.shape[-1] != d_k:
+        raise ValueError(f"Query and key must share d_k: {tuple(query.shape)} and {tuple(key.shape)}.")
+    lead = list(query.shape[:-2])
+    if list(key.shape[:-2]) != lead or list(value.shape[:-2]) != lead or key.shape[-2] != value.shape[-2]:
+        raise ValueError("query, key and value need the same leading axes and key/value the same length")
+    s_q, s_k, d_v = query.shape[-2], key.shape[-2], value.shape[-1]
+    if mask is not None:
+        _check_operand(mask, "mask")
+        if list(mask.shape) != [s_q, s_k]:
+            raise ValueError("mask must be (S_q, S_k)")
+    batch = 1
+    for d in lead:
+        batch *= d
+    out = torch.empty(lead + [s_q, d_v], dtype=torch.float32, device=query.device)
+    weights = torch.empty(lead + [s_q, s_k], dtype=torch.float32, device=query.device) if return_weights else None
+    if batch:
+        _lib.attention_forward(query, key, value, mask, out, weights, batch=batch, s_q=s_q, s_k=s_k, d_k=d_k,
+                               d_v=d_v, scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+    return (out, weights) if return_weights else out
+
+
 def conv2d(x, weight, bias=None, *, stride: int = 1, padding: int = 0, relu: bool = False,
            precision: int = _lib.PRECISION_3XTF32, stream=None):
     """``Conv2d::forward`` (src/conv.cpp:280-338): x (N, C, H, W), weight (outC, C, kH, kW), optional bias

@@ -20,6 +20,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "b200_gemm_f32",
+    "b200_attention_f32",
     "b200_conv2d_forward_f32",
     "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
@@ -70,6 +71,8 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_f32_fused.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
                                         c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f, c_int,
                                         ctypes.POINTER(Epilogue), c_vp, c_sz, c_vp]
+    lib.b200_attention_f32.restype = c_int
+    lib.b200_attention_f32.argtypes = [c_vp] * 6 + [c_i64] * 5 + [c_f, c_int, c_vp]
     lib.b200_conv2d_forward_f32.restype = c_int
     lib.b200_conv2d_forward_f32.argtypes = [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 9 + [c_int, c_int, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
@@ -157,6 +160,14 @@ def gemm_fused(A, B, C, *, batch: int, M: int, N: int, K: int, transA: bool = Fa
                                     lda, ldb, ldc, strideA, strideB, strideC, alpha, beta, precision,
                                     ctypes.byref(ep), _ptr(workspace), workspace_bytes, _stream_ptr(stream))
     _check(rc, "b200_gemm_f32_fused")
+
+
+def attention_forward(q, k, v, mask, out, weights, *, batch: int, s_q: int, s_k: int, d_k: int, d_v: int,
+                      scale: float, precision: int = PRECISION_3XTF32, stream=None) -> None:
+    """``out = softmax(q @ k^T * scale + mask) @ v`` per batch element, one fused kernel."""
+    rc = load().b200_attention_f32(_ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(out), _ptr(weights), batch, s_q,
+                                   s_k, d_k, d_v, scale, precision, _stream_ptr(stream))
+    _check(rc, "b200_attention_f32")
 
 
 def conv2d_forward(x, weight, bias, y, *, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int,

@@ -99,6 +99,20 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
                             int64_t kw, int64_t stride, int64_t pad, int relu, int precision,
                             void* stream);
 
+/* scaled_dot_product_attention as ONE kernel (src/transformer.cpp:279-304 composes it from a batched
+ * product against a materialised K^T, `* scale`, `+ mask`, Tensor::softmax, src/tensor_ops.cpp:621-647,
+ * and a second batched product; its softmax kernels are src/cuda/kernels.cu:835-895):
+ *     out[b] = softmax(q[b] x k[b]^T * scale + mask) x v[b]
+ * One CTA per batch element (= per head); the scores live in tensor memory and registers only, one
+ * query row per thread, and are normalised in the reference's order (max, exp, sequential fp32 sum,
+ * divide).  q: (batch, s_q, d_k); k: (batch, s_k, d_k); v: (batch, s_k, d_v); mask: (s_q, s_k)
+ * additive and shared by every batch element, or NULL; out: (batch, s_q, d_v); weights: optional
+ * (batch, s_q, s_k) copy of the softmax output (the reference's attention_weights), or NULL.
+ * Limits: s_q <= 128, s_k <= 128, d_k <= 64, d_v <= 64 (B200_ERANGE beyond; use the separate products). */
+int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
+                       float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                       float scale, int precision, void* stream);
+
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials
  * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */

@@ -8,6 +8,7 @@ Outputs (small, committed):
                        its gradients (tests/fixtures/matmul*.bin, consumed by
                        tests/test_reference.cpp:99-114), re-encoded as npz.
   pytorch_conv2d.npz   the reference's PyTorch golden vectors for Conv2d forward (tests/fixtures/conv2d_*.bin).
+  pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward (tests/fixtures/attention*.bin).
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
   reference_runs.npz   outputs of the UNMODIFIED reference engine (oracle/_ref) on seeded
                        inputs: its random streams, and per configuration a SHA-256 of the full
@@ -153,6 +154,16 @@ def main() -> None:
         for key in ("input", "weight", "bias", "output"):
             conv[f"{name}/{key}"] = fx[key]
     np.savez(HERE / "pytorch_conv2d.npz", **conv)
+
+    # 1c. the reference's PyTorch golden vectors for scaled dot-product attention
+    #     (tests/fixtures/attention*.bin, consumed by tests/test_reference.cpp:296-340)
+    att = {}
+    for name in ["attention", "attention_causal"]:
+        fx = read_fixture(ref_dir / "tests" / "fixtures" / f"{name}.bin")
+        for key, val in fx.items():
+            if not key.startswith("grad"):
+                att[f"{name}/{key}"] = val
+    np.savez(HERE / "pytorch_attention.npz", **att)
 
     # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
     known = [
