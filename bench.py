@@ -559,6 +559,30 @@ def run_engine_suite(args):
             "hbm_gbs_l2_flushed": round(bytes_alg / cold_us / 1e3, 1),
             "frac_of_measured_hbm": round(bytes_alg / cold_us / 1e3 / hbm, 4),
             "kernels_per_call": 2 if ws_bytes else 1}), flush=True)
+    # the attention core of the char-LM block: 128 heads of 64 x 24, causal mask — one fused kernel
+    # against the five separate steps (two products through this library, the rest through torch)
+    q, k, v = (torch.randn((32, 4, 64, 24), device=dev, generator=gen) for _ in range(3))
+    mask = torch.triu(torch.full((64, 64), -1e9, device=dev), 1)
+
+    def separate():
+        s_ = pkg.attention_scores(q, k, 24 ** -0.5, mask)
+        w_ = torch.softmax(s_, dim=-1)
+        return pkg.matmul(w_.reshape(128, 64, 64), v.reshape(128, 64, 24))
+
+    for label, fn, kernels in (("cfg2 attention core fused (32,4,64,24)", lambda: pkg.scaled_dot_product_attention(q, k, v, mask), 1),
+                               ("cfg2 attention core as 3 kernels (scores+mask, softmax, P.V)", separate, 3)):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(50):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        pkg.status()
+        print(json.dumps({"shape": label, "us_per_launch_back_to_back": round(e0.elapsed_time(e1) / 50 * 1e3, 2),
+                          "kernels_per_call": kernels,
+                          "note": "includes the output allocations by the Python wrapper"}), flush=True)
     # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel
     for name, n, c, h, w, out_c, k, stride, pad in CONV_SHAPES:
         x = torch.rand((n, c, h, w), device=dev, generator=gen)
