@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--no-extras", action="store_true", help="skip 4096^3, e2e and the CPU baseline")
     ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 peak measurement (profiling runs)")
-    ap.add_argument("--suite", default="", choices=["", "engine"],
+    ap.add_argument("--suite", default="", choices=["", "engine", "accuracy"],
                     help="'engine': time every GEMM of the char-LM, CNN and relu-sparse configurations "
                          "(one JSON line per shape) instead of the large-square benchmark")
     return ap.parse_args()
@@ -604,10 +604,67 @@ def run_engine_suite(args):
                           "note": "includes the output allocation by the Python wrapper"}), flush=True)
 
 
+def run_accuracy_suite(args):
+    """Error of the device result and of the reference's CPU loop against an fp64 product of the same
+    fp32 inputs (seeded with the reference's generator), for several promotion intervals and for
+    the TF32 mode.  One JSON line per configuration."""
+    import numpy as np
+    import torch
+
+    import __graft_entry__ as entry
+    from oracle import oracle_py as orc
+
+    pkg = entry.load_package()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+
+    def case(name, a, b):
+        A, B = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
+        M, K = a.shape
+        N = b.shape[1]
+        ref = A.double() @ B.double()
+        cpu = torch.from_numpy(orc.matmul(a, b)).to(dev)
+
+        def scaled(x, y=ref):
+            return float(((x.double() - y.double()).abs() / y.double().abs().clamp(min=1)).max().item())
+
+        def fro(x):
+            return float(((x.double() - ref).norm() / ref.norm()).item())
+
+        row = {"config": name, "M": M, "N": N, "K": K,
+               "cpu_loop_vs_fp64": {"scaled_max": scaled(cpu), "frobenius_rel": fro(cpu)}}
+        for pe in (1, 2, 4, 16):
+            pkg.set_option("promote_every", pe)
+            C = torch.empty((M, N), device=dev)
+            pkg.gemm(A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N)
+            pkg.status()
+            row[f"3xtf32_promote_every_{pe}"] = {"scaled_max_vs_fp64": scaled(C), "frobenius_rel_vs_fp64": fro(C),
+                                                 "scaled_max_vs_cpu_loop": scaled(C, cpu)}
+        pkg.set_option("promote_every", 1)
+        C = torch.empty((M, N), device=dev)
+        pkg.gemm(A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, precision=pkg.PRECISION_TF32)
+        pkg.status()
+        row["tf32"] = {"scaled_max_vs_fp64": scaled(C), "frobenius_rel_vs_fp64": fro(C)}
+        print(json.dumps(row), flush=True)
+
+    r = orc.Rng(0)
+    case("cfg1 512^3 U[-1,1] seed 0", r.rand((512, 512), -1, 1), r.rand((512, 512), -1, 1))
+    r = orc.Rng(2)
+    case("cfg2 2048x96x384 N(0,1) x Xavier seed 2", r.randn((2048, 96)), r.rand((96, 384), -0.1118, 0.1118))
+    r = orc.Rng(4)
+    a = np.maximum(r.randn((2048, 2048)), 0).astype(np.float32)
+    case("cfg4 2048^3 relu-sparse seed 4", a, r.randn((2048, 2048)))
+    r = orc.Rng(1)
+    case("cfg5 4096^3 N(0,1/K) seed 1", r.randn((4096, 4096), 0, 4096 ** -0.5), r.randn((4096, 4096), 0, 4096 ** -0.5))
+
+
 def main():
     args = parse_args()
     if args.suite == "engine":
         run_engine_suite(args)
+        return
+    if args.suite == "accuracy":
+        run_accuracy_suite(args)
         return
     if args.impl == "reference":
         run_reference(args)
