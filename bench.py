@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--no-extras", action="store_true", help="skip 4096^3, e2e and the CPU baseline")
+    ap.add_argument("--only", default="", help="with --suite engine: run only the shapes whose name contains this text")
     ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 peak measurement (profiling runs)")
     ap.add_argument("--suite", default="", choices=["", "engine", "accuracy"],
                     help="'engine': time every GEMM of the char-LM, CNN and relu-sparse configurations "
@@ -515,6 +516,8 @@ def run_engine_suite(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gen = torch.Generator(device=dev).manual_seed(2)
     for name, batch, M, N, K, tA, tB, ab, bb in ENGINE_SHAPES:
+        if args.only and args.only not in name:
+            continue
         a_shape = ((batch,) if ab else ()) + ((K, M) if tA else (M, K))
         b_shape = ((batch,) if bb else ()) + ((N, K) if tB else (K, N))
         A = torch.randn(a_shape, device=dev, generator=gen)
@@ -569,7 +572,7 @@ def run_engine_suite(args):
         w_ = torch.softmax(s_, dim=-1)
         return pkg.matmul(w_.reshape(128, 64, 64), v.reshape(128, 64, 24))
 
-    for label, fn, kernels in (("cfg2 attention core fused (32,4,64,24)", lambda: pkg.scaled_dot_product_attention(q, k, v, mask), 1),
+    for label, fn, kernels in () if (args.only and "attention" not in args.only) else (("cfg2 attention core fused (32,4,64,24)", lambda: pkg.scaled_dot_product_attention(q, k, v, mask), 1),
                                ("cfg2 attention core as 3 kernels (scores+mask, softmax, P.V)", separate, 3)):
         for _ in range(5):
             fn()
@@ -585,6 +588,8 @@ def run_engine_suite(args):
                           "note": "includes the output allocations by the Python wrapper"}), flush=True)
     # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel
     for name, n, c, h, w, out_c, k, stride, pad in CONV_SHAPES:
+        if args.only and args.only not in name:
+            continue
         x = torch.rand((n, c, h, w), device=dev, generator=gen)
         wt = torch.randn((out_c, c, k, k), device=dev, generator=gen)
         b = torch.randn((out_c,), device=dev, generator=gen)

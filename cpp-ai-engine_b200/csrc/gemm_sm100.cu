@@ -42,7 +42,6 @@ struct Options {
     long split_k = 0;
     long promote_every = 1;
     long force_ldg = 0;
-    long k_block = 32;
     long pair_mode = 0;  // 0 automatic, 1 never, 2 whenever legal
     long host_pipeline = 1;  // b200_matmul_f32_host: overlap transfers with the math
     long tail_split = 1;     // split the tiles of a mostly-empty last wave along K
@@ -257,7 +256,6 @@ int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& m
 #define B200_CASE(BN_)                                                                     \
     case BN_:                                                                              \
         if (!tma) return launch_cfg<BN_, 32, false>(p, ma, mb, grid, stream);              \
-        if (bk == 16) return launch_cfg<BN_, 16, true>(p, ma, mb, grid, stream);           \
         return launch_cfg<BN_, 32, true>(p, ma, mb, grid, stream);
     switch (bn) {
         B200_CASE(32)
@@ -286,7 +284,7 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
                size_t workspace_bytes) {
     Plan pl{};
     pl.tma = tma_ok && !g_opt.force_ldg;
-    pl.bk = (pl.tma && g_opt.k_block == 16) ? 16 : 32;
+    pl.bk = 32;
     pl.tiles_m = ceil_div(M, kBM);
     const int sms = st.sm_count > 0 ? st.sm_count : 148;
     int bn = 32;
@@ -890,18 +888,51 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
     }
 }
 
-int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
-                       float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
-                       float scale, int precision, void* stream) {
+}  // extern "C"
+
+namespace {
+template <int CH>
+cudaError_t launch_attention(const b200::AttnParams& p, int grid, uint32_t smem, cudaStream_t stream) {
+    static uint32_t attr_bytes[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > attr_bytes[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(b200::attention_fwd_kernel<CH>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_bytes[dev] = smem;
+    }
+    b200::attention_fwd_kernel<CH><<<grid, b200::kAttnThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+}  // namespace
+
+extern "C" {
+
+#ifdef B200_ATTN_PROFILE
+static long long* g_attn_prof = nullptr;
+void b200_dev_set_attn_prof(long long* buf) { g_attn_prof = buf; }
+#endif
+
+int b200_attention_f32_strided(const float* q, const float* k, const float* v, const float* mask,
+                               float* out, float* weights, int64_t batch, int64_t heads, int64_t s_q,
+                               int64_t s_k, int64_t d_k, int64_t d_v, const int64_t q_strides[3],
+                               const int64_t k_strides[3], const int64_t v_strides[3],
+                               const int64_t out_strides[3], float scale, int precision, void* stream) {
     DeviceState* st = nullptr;
     int rc = device_state(&st);
     if (rc) return rc;
-    if (batch < 0 || s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
+    if (batch < 0 || heads <= 0 || s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
     if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (q_strides == nullptr || k_strides == nullptr || v_strides == nullptr || out_strides == nullptr)
+        return B200_EINVAL;
+    if (q_strides[2] < d_k || k_strides[2] < d_k || v_strides[2] < d_v || out_strides[2] < d_v) return B200_EINVAL;
+    for (int i = 0; i < 2; ++i)
+        if (q_strides[i] < 0 || k_strides[i] < 0 || v_strides[i] < 0 || out_strides[i] < 0) return B200_EINVAL;
     if (s_q > 128 || s_k > kAttnMaxSk || d_k > kAttnMaxD || d_v > kAttnMaxD) return B200_ERANGE;
     if (batch == 0) return B200_OK;
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return B200_EINVAL;
-    if (batch > 0x7fffffffll) return B200_ERANGE;
+    if (batch > 0x7fffffffll / heads) return B200_ERANGE;
     AttnParams p{};
     p.q = q;
     p.k = k;
@@ -909,7 +940,12 @@ int b200_attention_f32(const float* q, const float* k, const float* v, const flo
     p.mask = mask;
     p.out = out;
     p.weights = weights;
-    p.batch = static_cast<int>(batch);
+    p.q_bs = q_strides[0], p.q_hs = q_strides[1], p.q_ld = q_strides[2];
+    p.k_bs = k_strides[0], p.k_hs = k_strides[1], p.k_ld = k_strides[2];
+    p.v_bs = v_strides[0], p.v_hs = v_strides[1], p.v_ld = v_strides[2];
+    p.o_bs = out_strides[0], p.o_hs = out_strides[1], p.o_ld = out_strides[2];
+    p.batch = static_cast<int>(batch * heads);
+    p.heads = static_cast<int>(heads);
     p.s_q = static_cast<int>(s_q);
     p.s_k = static_cast<int>(s_k);
     p.d_k = static_cast<int>(d_k);
@@ -920,23 +956,34 @@ int b200_attention_f32(const float* q, const float* k, const float* v, const flo
     p.scale = scale;
     p.precision = precision;
     p.status = st->status;
+#ifdef B200_ATTN_PROFILE
+    p.prof = g_attn_prof;
+#endif
     const uint32_t q_bytes = 128u * p.dk_pad * 4u, k_bytes = static_cast<uint32_t>(p.sk_pad) * p.dk_pad * 4u;
     const uint32_t p_bytes = 128u * p.sk_pad * 4u, v_bytes = static_cast<uint32_t>(p.dv_pad) * p.sk_pad * 4u;
     const uint32_t region1 = std::max(2 * (q_bytes + k_bytes), 2 * p_bytes);
     const uint32_t smem = region1 + 2 * v_bytes + 1024;
-    static uint32_t attr_bytes[kMaxDevices] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (smem > attr_bytes[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        attr_bytes[dev] = smem;
+    const int grid = static_cast<int>(std::min<int64_t>(p.batch, st->sm_count));
+    cudaError_t e = cudaSuccess;
+    switch (p.sk_pad / 32) {
+        case 1: e = launch_attention<1>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        case 2: e = launch_attention<2>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        case 3: e = launch_attention<3>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        default: e = launch_attention<4>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
     }
-    const int grid = static_cast<int>(std::min<int64_t>(batch, 2 * st->sm_count));
-    attention_fwd_kernel<<<grid, kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    if (e != cudaSuccess) return static_cast<int>(e);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return static_cast<int>(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
+                       float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                       float scale, int precision, void* stream) {
+    if (s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
+    const int64_t qs[3] = {s_q * d_k, 0, d_k}, ks[3] = {s_k * d_k, 0, d_k};
+    const int64_t vs[3] = {s_k * d_v, 0, d_v}, os[3] = {s_q * d_v, 0, d_v};
+    return b200_attention_f32_strided(q, k, v, mask, out, weights, batch, 1, s_q, s_k, d_k, d_v, qs, ks, vs, os,
+                                      scale, precision, stream);
 }
 
 int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,
@@ -1029,9 +1076,6 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "pair_mode")) {
         if (value < 0 || value > 2) return B200_EINVAL;
         g_opt.pair_mode = value;
-    } else if (!std::strcmp(name, "k_block")) {
-        if (value != 16 && value != 32) return B200_EINVAL;
-        g_opt.k_block = value;
     } else {
         return B200_EINVAL;
     }

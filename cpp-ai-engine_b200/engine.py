@@ -233,6 +233,53 @@ def scaled_dot_product_attention(query, key, value, mask=None, *, return_weights
     return (out, weights) if return_weights else out
 
 
+def multi_head_attention_core(query, key, value, num_heads: int, mask=None, *, return_weights: bool = False,
+                              precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """The middle of ``MultiHeadAttention::forward`` (src/transformer.cpp:339-357): from the three projections
+    (B, S, d_model) to the merged context (B, S, d_model).  The reference materialises
+    ``reshape(B, S, H, hd).permute(0, 2, 1, 3)`` three times and the inverse permute once; here the fused
+    attention kernel reads each head through strides and writes the merged layout directly.  The projections
+    may be column slices of one wider tensor (a fused Q|K|V product): only the last axis must be dense.
+    Returns ``merged`` or ``(merged, attention_weights)`` with the weights shaped (B, H, S_q, S_k)."""
+    import math
+
+    import torch
+
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a torch tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must live on a CUDA device: there is no CPU path")
+        if t.dtype != torch.float32:
+            raise TypeError(f"{name} must be float32")
+        if t.dim() != 3:
+            raise ValueError(f"MultiHeadAttention expects (batch, seq, d_model), received {tuple(t.shape)}.")
+        if t.stride(2) != 1:
+            raise ValueError(f"{name} must be dense along its last axis")
+    if num_heads <= 0 or query.shape[2] % num_heads != 0 or value.shape[2] % num_heads != 0:
+        raise ValueError("d_model must be divisible by num_heads.")
+    batch, s_q, d_model = query.shape
+    if key.shape[0] != batch or value.shape[0] != batch or key.shape[2] != d_model or key.shape[1] != value.shape[1]:
+        raise ValueError("query, key and value need the same batch, key/value the same length and query/key the "
+                         "same width")
+    s_k = key.shape[1]
+    d_k, d_v = d_model // num_heads, value.shape[2] // num_heads
+    if mask is not None:
+        _check_operand(mask, "mask")
+        if list(mask.shape) != [s_q, s_k]:
+            raise ValueError("mask must be (S_q, S_k)")
+    out = torch.empty((batch, s_q, num_heads * d_v), dtype=torch.float32, device=query.device)
+    weights = (torch.empty((batch, num_heads, s_q, s_k), dtype=torch.float32, device=query.device)
+               if return_weights else None)
+    if batch:
+        _lib.attention_forward_strided(
+            query, key, value, mask, out, weights, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
+            q_strides=(query.stride(0), d_k, query.stride(1)), k_strides=(key.stride(0), d_k, key.stride(1)),
+            v_strides=(value.stride(0), d_v, value.stride(1)), out_strides=(out.stride(0), d_v, out.stride(1)),
+            scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+    return (out, weights) if return_weights else out
+
+
 def conv2d(x, weight, bias=None, *, stride: int = 1, padding: int = 0, relu: bool = False,
            precision: int = _lib.PRECISION_3XTF32, stream=None):
     """``Conv2d::forward`` (src/conv.cpp:280-338): x (N, C, H, W), weight (outC, C, kH, kW), optional bias

@@ -21,6 +21,7 @@ _lib: Optional[ctypes.CDLL] = None
 EXPORTS = (
     "b200_gemm_f32",
     "b200_attention_f32",
+    "b200_attention_f32_strided",
     "b200_conv2d_forward_f32",
     "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
@@ -73,6 +74,9 @@ def load() -> ctypes.CDLL:
                                         ctypes.POINTER(Epilogue), c_vp, c_sz, c_vp]
     lib.b200_attention_f32.restype = c_int
     lib.b200_attention_f32.argtypes = [c_vp] * 6 + [c_i64] * 5 + [c_f, c_int, c_vp]
+    lib.b200_attention_f32_strided.restype = c_int
+    lib.b200_attention_f32_strided.argtypes = ([c_vp] * 6 + [c_i64] * 6 + [ctypes.POINTER(c_i64)] * 4
+                                               + [c_f, c_int, c_vp])
     lib.b200_conv2d_forward_f32.restype = c_int
     lib.b200_conv2d_forward_f32.argtypes = [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 9 + [c_int, c_int, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
@@ -168,6 +172,19 @@ def attention_forward(q, k, v, mask, out, weights, *, batch: int, s_q: int, s_k:
     rc = load().b200_attention_f32(_ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(out), _ptr(weights), batch, s_q,
                                    s_k, d_k, d_v, scale, precision, _stream_ptr(stream))
     _check(rc, "b200_attention_f32")
+
+
+def attention_forward_strided(q, k, v, mask, out, weights, *, batch: int, heads: int, s_q: int, s_k: int, d_k: int,
+                              d_v: int, q_strides, k_strides, v_strides, out_strides, scale: float,
+                              precision: int = PRECISION_3XTF32, stream=None) -> None:
+    """The fused attention kernel over ``batch * heads`` matrices addressed by (batch, head, row) strides in
+    floats: the split into heads and the merge back cost no copy."""
+    arr = ctypes.c_int64 * 3
+    rc = load().b200_attention_f32_strided(_ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(out), _ptr(weights), batch,
+                                           heads, s_q, s_k, d_k, d_v, arr(*q_strides), arr(*k_strides),
+                                           arr(*v_strides), arr(*out_strides), scale, precision,
+                                           _stream_ptr(stream))
+    _check(rc, "b200_attention_f32_strided")
 
 
 def conv2d_forward(x, weight, bias, y, *, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int,

@@ -103,15 +103,29 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
  * product against a materialised K^T, `* scale`, `+ mask`, Tensor::softmax, src/tensor_ops.cpp:621-647,
  * and a second batched product; its softmax kernels are src/cuda/kernels.cu:835-895):
  *     out[b] = softmax(q[b] x k[b]^T * scale + mask) x v[b]
- * One CTA per batch element (= per head); the scores live in tensor memory and registers only, one
- * query row per thread, and are normalised in the reference's order (max, exp, sequential fp32 sum,
- * divide).  q: (batch, s_q, d_k); k: (batch, s_k, d_k); v: (batch, s_k, d_v); mask: (s_q, s_k)
+ * One CTA per batch element (= per head); the scores live in tensor memory and registers only, two
+ * threads per query row, and are normalised in the reference's order (max, exp, fp32 sum over the
+ * columns in ascending order, divide).  q: (batch, s_q, d_k); k: (batch, s_k, d_k); v: (batch, s_k, d_v); mask: (s_q, s_k)
  * additive and shared by every batch element, or NULL; out: (batch, s_q, d_v); weights: optional
  * (batch, s_q, s_k) copy of the softmax output (the reference's attention_weights), or NULL.
  * Limits: s_q <= 128, s_k <= 128, d_k <= 64, d_v <= 64 (B200_ERANGE beyond; use the separate products). */
 int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
                        float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
                        float scale, int precision, void* stream);
+
+/* b200_attention_f32 on the head-split VIEW of the projections, writing the merged layout
+ * (MultiHeadAttention::forward, src/transformer.cpp:339-357, materialises
+ * reshape(B, S, H, hd).permute(0, 2, 1, 3) for q, k and v and the inverse permute for the result;
+ * here both are addressing).  There are batch * heads matrices; element (row, e) of matrix (b, h) of
+ * q lies at q[b * q_strides[0] + h * q_strides[1] + row * q_strides[2] + e] (strides in floats, the
+ * last axis contiguous), likewise k, v and out.  For projections stored (B, S, H * hd):
+ * strides = {S * H * hd, hd, H * hd}.  weights, if given, is (batch * heads, s_q, s_k) contiguous.
+ * Same limits and errors as b200_attention_f32. */
+int b200_attention_f32_strided(const float* q, const float* k, const float* v, const float* mask,
+                               float* out, float* weights, int64_t batch, int64_t heads, int64_t s_q,
+                               int64_t s_k, int64_t d_k, int64_t d_v, const int64_t q_strides[3],
+                               const int64_t k_strides[3], const int64_t v_strides[3],
+                               const int64_t out_strides[3], float scale, int precision, void* stream);
 
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials
@@ -194,7 +208,6 @@ uint64_t b200_gemm_launch_count(void);
  *   "split_k"       0 = automatic, 1 = never split, n = force n splits (needs workspace)
  *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
- *   "k_block"       32 (default) or 16: values of k per shared-memory stage on the TMA path
  *   "group_m"       tile rows per scheduling band (0 = automatic: 8 for pair tiles, 16 otherwise)
  *   "tail_split"    1 (default) = when the last wave of tiles would leave most SMs idle, run its
  *                   tiles split along K in a second launch (needs workspace), 0 = never

@@ -9,6 +9,7 @@ Outputs (small, committed):
                        tests/test_reference.cpp:99-114), re-encoded as npz.
   pytorch_conv2d.npz   the reference's PyTorch golden vectors for Conv2d forward (tests/fixtures/conv2d_*.bin).
   pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward (tests/fixtures/attention*.bin).
+  pytorch_multihead.npz  the same for a whole MultiHeadAttention forward (tests/fixtures/multihead_attention.bin).
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
   reference_runs.npz   outputs of the UNMODIFIED reference engine (oracle/_ref) on seeded
                        inputs: its random streams, and per configuration a SHA-256 of the full
@@ -164,6 +165,12 @@ def main() -> None:
             if not key.startswith("grad"):
                 att[f"{name}/{key}"] = val
     np.savez(HERE / "pytorch_attention.npz", **att)
+
+    # 1d. the reference's PyTorch golden vectors for MultiHeadAttention(8, 2) forward
+    #     (tests/fixtures/multihead_attention.bin, consumed by tests/test_reference.cpp:322-349):
+    #     input, the four projections' weights (in, out) and biases, output
+    fx = read_fixture(ref_dir / "tests" / "fixtures" / "multihead_attention.bin")
+    np.savez(HERE / "pytorch_multihead.npz", **{k: v for k, v in fx.items() if not k.startswith("grad")})
 
     # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
     known = [

@@ -79,3 +79,90 @@ def test_limits_are_reported_not_silently_wrong(pkg, cuda):
     with pytest.raises(ValueError):
         pkg.scaled_dot_product_attention(torch.zeros((2, 4, 8), device=cuda), torch.zeros((2, 4, 6), device=cuda),
                                          torch.zeros((2, 4, 6), device=cuda))
+
+
+# ---------------------------------------------------------------------------------------------
+# Heads addressed through strides: MultiHeadAttention::forward without its permute copies
+# (src/transformer.cpp:339-357)
+# ---------------------------------------------------------------------------------------------
+
+def split_heads(t, heads):
+    b, s, dm = t.shape
+    return np.ascontiguousarray(t.reshape(b, s, heads, dm // heads).transpose(0, 2, 1, 3))
+
+
+@pytest.mark.parametrize("dims", [
+    # (batch, heads, s_q, s_k, head_dim)
+    (32, 4, 64, 64, 24),   # the char-LM block
+    (2, 2, 5, 5, 4),       # the reference's MultiHeadAttention(8, 2) fixture shape
+    (3, 5, 17, 33, 9),     # nothing aligned
+    (1, 1, 128, 128, 64),  # the kernel's limits
+])
+@pytest.mark.parametrize("causal", [False, True])
+def test_strided_heads_equal_permuted_copies(pkg, cuda, orc, dims, causal):
+    """The strided entry point on (B, S, H*hd) projections gives, bit for bit, what the contiguous entry
+    point gives on the materialised (B, H, S, hd) permutes, merged back — and both match the reference's
+    sequence."""
+    b, heads, s_q, s_k, hd = dims
+    g = orc.Rng(71)
+    q, k, v = g.randn((b, s_q, heads * hd)), g.randn((b, s_k, heads * hd)), g.randn((b, s_k, heads * hd))
+    mask = np.triu(np.full((s_q, s_k), -1e9, np.float32), 1) if causal else None
+    dmask = dev(mask, cuda) if causal else None
+    before = pkg.launch_count()
+    merged, w = pkg.multi_head_attention_core(dev(q, cuda), dev(k, cuda), dev(v, cuda), heads, dmask,
+                                              return_weights=True)
+    pkg.status()
+    assert pkg.launch_count() == before + 1
+    out4, w4 = pkg.scaled_dot_product_attention(dev(split_heads(q, heads), cuda), dev(split_heads(k, heads), cuda),
+                                                dev(split_heads(v, heads), cuda), dmask, return_weights=True)
+    pkg.status()
+    want_merged = out4.permute(0, 2, 1, 3).reshape(b, s_q, heads * hd)
+    assert np.array_equal(merged.cpu().numpy(), want_merged.cpu().numpy())
+    assert np.array_equal(w.cpu().numpy(), w4.cpu().numpy())
+    ref_out, _ = reference_attention(orc, split_heads(q, heads), split_heads(k, heads), split_heads(v, heads), mask)
+    ref_merged = ref_out.transpose(0, 2, 1, 3).reshape(b, s_q, heads * hd)
+    assert orc.scaled_error(merged.cpu().numpy(), ref_merged) <= 1e-5
+
+
+def test_strided_heads_on_fused_qkv_slices(pkg, cuda, orc):
+    """q, k and v as column slices of ONE (B, S, 3*d_model) product (row stride 3*d_model)."""
+    import torch
+
+    b, heads, s, hd = 4, 4, 64, 24
+    dm = heads * hd
+    g = orc.Rng(72)
+    qkv = dev(g.randn((b, s, 3 * dm)), cuda)
+    q, k, v = qkv[:, :, :dm], qkv[:, :, dm:2 * dm], qkv[:, :, 2 * dm:]
+    got = pkg.multi_head_attention_core(q, k, v, heads)
+    pkg.status()
+    want = pkg.multi_head_attention_core(q.contiguous(), k.contiguous(), v.contiguous(), heads)
+    pkg.status()
+    assert torch.equal(got, want)
+
+
+def test_pytorch_golden_multihead(pkg, cuda, golden_dir):
+    """The reference's PyTorch vectors for a whole MultiHeadAttention(8, 2) forward
+    (tests/test_reference.cpp:322-339, abs 1e-4): four Linear layers around the strided core."""
+    z = np.load(golden_dir / "pytorch_multihead.npz")
+    x = dev(z["input"], cuda)
+    proj = {}
+    for tag in ("query", "key", "value"):
+        proj[tag] = pkg.linear(x, dev(z[f"w.{tag}.weight"], cuda), dev(z[f"w.{tag}.bias"].reshape(-1), cuda))
+    merged = pkg.multi_head_attention_core(proj["query"], proj["key"], proj["value"], 2)
+    out = pkg.linear(merged, dev(z["w.out.weight"], cuda), dev(z["w.out.bias"].reshape(-1), cuda))
+    pkg.status()
+    assert np.max(np.abs(out.cpu().numpy() - z["output"])) <= 1e-4
+
+
+def test_strided_argument_errors(pkg, cuda):
+    import torch
+
+    x = torch.zeros((2, 8, 12), device=cuda)
+    with pytest.raises(ValueError):
+        pkg.multi_head_attention_core(x, x, x, 5)              # d_model not divisible by heads
+    with pytest.raises(ValueError):
+        pkg.multi_head_attention_core(x, x[:, :, :8], x, 2)    # query/key widths differ
+    with pytest.raises(ValueError):
+        pkg.multi_head_attention_core(x[0], x[0], x[0], 2)     # not (batch, seq, d_model)
+    with pytest.raises(ValueError):
+        pkg.multi_head_attention_core(x.transpose(1, 2), x.transpose(1, 2), x.transpose(1, 2), 2)  # last axis strided
