@@ -80,6 +80,8 @@ struct GemmParams {
     // implicit-GEMM convolution (conv kernels only): A is gathered from an NCHW input instead of a
     // stored column matrix, and the output is stored NCHW
     int cv_c, cv_h, cv_w, cv_kh, cv_kw, cv_stride, cv_pad, cv_oh, cv_ow;
+    int cv_oc;        // output channels of the convolution (gradient kernels)
+    int cv_store_hw;  // pixels per image and channel of the tensor the NCHW store writes
     int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
     int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
     int* status;
@@ -316,7 +318,191 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
     }
 }
 
-template <int BN, int BK, bool kTma, bool kPair = false, bool kConv = false>
+// Stores one unit (4 consecutive k of one tile row) of a K-major swizzled tile, split.
+__device__ __forceinline__ void store_unit_split(uint8_t* hi, uint8_t* lo, bool want_lo, int r, int c,
+                                                 const float4& v) {
+    const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (uint32_t)((c ^ (r & 7)) << 4);
+    float4 h, l;
+    tf32_split(v.x, h.x, l.x);
+    tf32_split(v.y, h.y, l.y);
+    tf32_split(v.z, h.z, l.z);
+    tf32_split(v.w, h.w, l.w);
+    *reinterpret_cast<float4*>(hi + off) = h;
+    if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
+}
+
+// Weight gradient of a convolution, dW (outC x C*kH*kW) = dOut^T x cols, with neither dOut^T nor
+// cols ever written (the reference's backward of `cols.matmul(W^T)`, src/tensor_ops.cpp:570-585,
+// materialises cols^T and multiplies by the (N*spatial, outC) gradient).  The contraction runs
+// over the output positions m = (n, oh, ow).
+//
+// A tile: row = output channel o, k = m, read from dy (N, outC, oH, oW): for one channel,
+// consecutive m of an image are consecutive floats.  Rows past outC are left as they are: they
+// feed accumulator rows that are never stored.
+__device__ __forceinline__ void conv_dy_rows_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
+                                                         uint8_t* lo, bool want_lo, int wtid) {
+    constexpr int kPer = kBM * 8 / kWorkerThreads;
+    const int ohw = p.cv_oh * p.cv_ow;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        const int o = row0 + r, m0 = k0 + c * 4;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (o < p.M && m0 < p.K) {
+            const int img = m0 / ohw, sp = m0 - img * ohw;
+            const float* src = p.A + ((long long)img * p.M + o) * ohw + sp;
+            if (p.a_vec_ok) {  // ohw % 4 == 0: the four positions lie in one image, 16-byte aligned
+                const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+                x4[0] = t.x, x4[1] = t.y, x4[2] = t.z, x4[3] = t.w;
+            } else {
+                int ii = img, ss = sp;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (m0 + e < p.K) x4[e] = __ldg(p.A + ((long long)ii * p.M + o) * ohw + ss);
+                    if (++ss == ohw) ss = 0, ++ii;
+                }
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        if (row0 + r < p.M) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    }
+}
+
+// B tile of the weight gradient: row = column kc = (c, kh, kw) of the column matrix, k = m,
+// gathered from x (N, C, H, W) exactly as nn::im2col would have filled cols[m][kc]
+// (src/conv.cpp:61-150).  Rows past C*kH*kW are left as they are (columns that are never stored).
+template <int ROWS>
+__device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
+                                                        uint8_t* lo, bool want_lo, int wtid) {
+    constexpr int kPer = ROWS * 8 / kWorkerThreads;
+    const int ohw = p.cv_oh * p.cv_ow, khw = p.cv_kh * p.cv_kw;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        const int kc = row0 + r, m0 = k0 + c * 4;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (kc < p.N && m0 < p.K) {
+            const int ci = kc / khw, rem = kc - ci * khw;
+            const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+            int img = m0 / ohw;
+            const int pix = m0 - img * ohw;
+            int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (m0 + e < p.K) {
+                    const int ih = oh * p.cv_stride - p.cv_pad + kh, iw = ow * p.cv_stride - p.cv_pad + kw;
+                    if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w)
+                        x4[e] = __ldg(p.B + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
+                }
+                if (++ow == p.cv_ow) {
+                    ow = 0;
+                    if (++oh == p.cv_oh) oh = 0, ++img;
+                }
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    }
+}
+
+// Input gradient of a convolution as ONE gather product (the reference forms dCols = dOut x W and
+// scatters it with col2im, src/conv.cpp:152-222, summing the overlaps):
+//   dx[n][c][ih][iw] = sum over (o, kh, kw) of dy[n][o][(ih+pad-kh)/s][(iw+pad-kw)/s] * W[o][c][kh][kw]
+// taken over the terms whose divisions are exact and land inside dy.
+//
+// A tile: row = input pixel m' = (n, ih, iw), k = (o, kh, kw), gathered from dy.
+__device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
+                                                           uint8_t* lo, bool want_lo, int wtid) {
+    constexpr int kPer = kBM * 8 / kWorkerThreads;
+    const int hw = p.cv_h * p.cv_w, khw = p.cv_kh * p.cv_kw;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit % kBM, c = unit / kBM;
+        const int gr = row0 + r;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (gr < p.M) {
+            const int img = gr / hw, pix = gr - img * hw;
+            const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int gk = k0 + c * 4 + e;
+                if (gk < p.K) {
+                    const int o = gk / khw, rem = gk - o * khw;
+                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    int ty = ih + p.cv_pad - kh, tx = iw + p.cv_pad - kw;
+                    bool hit = ty >= 0 && tx >= 0;
+                    if (p.cv_stride != 1 && hit) {
+                        const int oy = ty / p.cv_stride, ox = tx / p.cv_stride;
+                        hit = oy * p.cv_stride == ty && ox * p.cv_stride == tx;
+                        ty = oy, tx = ox;
+                    }
+                    if (hit && ty < p.cv_oh && tx < p.cv_ow)
+                        x4[e] = __ldg(p.A + (((long long)img * p.cv_oc + o) * p.cv_oh + ty) * p.cv_ow + tx);
+                }
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        store_unit_split(hi, lo, want_lo, unit % kBM, unit / kBM, v[u]);
+    }
+}
+
+// B tile of the input gradient: row = input channel c, k = (o, kh, kw), read from the weight
+// (outC, C, kH, kW) as it is stored.  Rows past C are left as they are.
+template <int ROWS>
+__device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
+                                                          uint8_t* lo, bool want_lo, int wtid) {
+    constexpr int kPer = ROWS * 8 / kWorkerThreads;
+    const int khw = p.cv_kh * p.cv_kw;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        const int ci = row0 + r;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (ci < p.N) {
+            int gk = k0 + c * 4;
+            int o = gk / khw, q = gk - o * khw;
+#pragma unroll
+            for (int e = 0; e < 4; ++e, ++gk) {
+                if (gk < p.K) x4[e] = __ldg(p.B + ((long long)o * p.cv_c + ci) * khw + q);
+                if (++q == khw) q = 0, ++o;
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int unit = wtid + u * kWorkerThreads;
+        const int r = unit >> 3, c = unit & 7;
+        if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    }
+}
+
+// kConv: 0 a plain product; 1 convolution forward (A gathered from x, NCHW store); 2 weight
+// gradient (both operands gathered, contraction over the output positions, plain store);
+// 3 input gradient (A gathered from dy, B from the weight, NCHW store).
+template <int BN, int BK, bool kTma, bool kPair = false, int kConv = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                  const __grid_constant__ CUtensorMap mapB) {
@@ -327,7 +513,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     constexpr int kArrivals = kPair ? 2 * kWorkerWarps : kWorkerWarps;
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
     static_assert(!kPair || kTma, "pair mode loads with TMA");
-    static_assert(!kConv || !kTma, "the convolution gathers its A operand in registers");
+    static_assert(kConv == 0 || !kTma, "the convolution gathers its operands in registers");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -650,15 +836,27 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const int k0 = (wk.kb0 + i) * BK;
                     const float* a_base = p.A + (long long)wk.b * p.strideA;
                     const float* b_base = p.B + (long long)wk.b * p.strideB;
-                    if constexpr (kConv) {
+                    if constexpr (kConv == 1) {
                         conv_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                    } else if constexpr (kConv == 2) {
+                        conv_dy_rows_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                    } else if constexpr (kConv == 3) {
+                        conv_dx_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
                     } else {
                         ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
                                              p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
                     }
-                    ldg_split_store<BN>(b_base, p.ldb, p.transB != 0, p.b_vec_ok != 0, wk.nt * BN,
-                                        p.N, k0, p.K, stage + Cfg::kABytes,
-                                        stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
+                    if constexpr (kConv == 2) {
+                        conv_cols_T_split_store<BN>(p, wk.nt * BN, k0, stage + Cfg::kABytes,
+                                                    stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
+                    } else if constexpr (kConv == 3) {
+                        conv_weight_T_split_store<BN>(p, wk.nt * BN, k0, stage + Cfg::kABytes,
+                                                      stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
+                    } else {
+                        ldg_split_store<BN>(b_base, p.ldb, p.transB != 0, p.b_vec_ok != 0, wk.nt * BN,
+                                            p.N, k0, p.K, stage + Cfg::kABytes,
+                                            stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
+                    }
                 }
                 // generic-proxy writes -> visible to the tensor core's async-proxy reads
                 fence_proxy_async_smem();
@@ -689,15 +887,16 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores rows:
             // one instruction writes four full 128-byte row segments — what HBM and, for the
             // peers' copies of C, NVLink want.
-            if constexpr (kConv) {
-                // The product's row m = (n, oh, ow) and column oc go to y[n][oc][oh][ow]: for one
+            if constexpr (kConv == 1 || kConv == 3) {
+                // The product's row m = (n, pixel) and column ch go to t[n][ch][pixel]: for one
                 // column, the 32 rows a warp holds are 32 consecutive floats, so the threads store
                 // their own registers directly and the (N, spatial, C) -> (N, C, H, W) permute of
-                // Conv2d::forward (src/conv.cpp:335-337) never happens as a separate pass.
+                // Conv2d::forward (src/conv.cpp:335-337) — or, for the input gradient, col2im's
+                // scatter — never happens as a separate pass.
                 const int row = wk.mt * kBM + quarter * 32 + lane;
                 const int col_base = wk.nt * BN + half * kCols;
                 if (row < p.M) {
-                    const int ohw = p.cv_oh * p.cv_ow;
+                    const int ohw = p.cv_store_hw;
                     const int img = row / ohw, pix = row - img * ohw;
                     float* ybase = p.dest[0] + (long long)img * p.N * ohw + pix;
 #pragma unroll
@@ -706,6 +905,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         if (col < p.N) {
                             float o = p.alpha * acc[j];
                             if (p.bias) o += __ldg(p.bias + col);
+                            if (p.beta != 0.f) o += p.beta * ybase[(long long)col * ohw];
                             if (p.relu) o = fmaxf(o, 0.f);
                             ybase[(long long)col * ohw] = o;
                         }

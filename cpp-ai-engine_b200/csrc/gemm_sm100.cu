@@ -231,14 +231,15 @@ int launch_pair(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& m
     return static_cast<int>(e);
 }
 
-// Convolution kernels: register-staged loader with the implicit im2col gather.
-template <int BN>
+// Convolution kernels: register-staged loader with the implicit im2col gather (MODE 1 forward,
+// 2 weight gradient, 3 input gradient).
+template <int BN, int MODE = 1>
 int launch_conv_cfg(const GemmParams& p, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN, 32>;
     static bool attr_set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = gemm_tf32_kernel<BN, 32, false, false, true>;
+    auto kernel = gemm_tf32_kernel<BN, 32, false, false, MODE>;
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(Cfg::kSmemBytes));
@@ -249,6 +250,73 @@ int launch_conv_cfg(const GemmParams& p, int grid, cudaStream_t stream) {
     kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p, unused, unused);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
+}
+
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+template <int MODE>
+int launch_conv(int bn, const GemmParams& p, int grid, cudaStream_t stream) {
+    switch (bn) {
+        case 32: return launch_conv_cfg<32, MODE>(p, grid, stream);
+        case 64: return launch_conv_cfg<64, MODE>(p, grid, stream);
+        case 128: return launch_conv_cfg<128, MODE>(p, grid, stream);
+        default: return launch_conv_cfg<256, MODE>(p, grid, stream);
+    }
+}
+
+// Narrowest tile that covers `cols` output columns while filling the SMs, as for any narrow product.
+int conv_tile_n(const DeviceState& st, int64_t rows, int64_t cols) {
+    int bn = 32;
+    for (int cand : {256, 128, 64, 32}) {
+        if (cand > 32 && cols <= cand / 2) continue;
+        const int64_t tiles = ceil_div(rows, kBM) * static_cast<int64_t>(ceil_div(cols, cand));
+        bn = cand;
+        if (tiles >= st.sm_count) break;
+    }
+    return bn;
+}
+
+// The weight gradient contracts over the n * oh * ow output positions into a small
+// (out_c x c*kh*kw) result: its k-blocks are shared out over the SMs (deterministic split-K).
+struct ConvDwPlan {
+    int bn, tiles_m, tiles_n, kblocks, split_k, kb_per_split;
+    size_t bytes;  // split-K partials
+};
+ConvDwPlan conv_dw_plan(const DeviceState& st, int64_t positions, int64_t out_c, int64_t kcols) {
+    ConvDwPlan pl{};
+    pl.bn = conv_tile_n(st, out_c, kcols);
+    pl.tiles_m = ceil_div(out_c, kBM);
+    pl.tiles_n = ceil_div(kcols, pl.bn);
+    pl.kblocks = ceil_div(positions, 32);
+    const int tiles = pl.tiles_m * pl.tiles_n;
+    int split = st.sm_count / (tiles > 0 ? tiles : 1);
+    if (split > pl.kblocks / 2) split = pl.kblocks / 2;  // at least two k-blocks per part
+    if (split < 1) split = 1;
+    pl.kb_per_split = ceil_div(pl.kblocks, split);
+    pl.split_k = ceil_div(pl.kblocks, pl.kb_per_split);
+    pl.bytes = pl.split_k > 1 ? static_cast<size_t>(pl.split_k) * out_c * kcols * sizeof(float) : 0;
+    return pl;
+}
+
+// dbias[o] = sum over (n, oh, ow) of dy[n][o][oh][ow] (+ beta * dbias[o]): one block per channel,
+// fixed summation order.
+__global__ void conv_bias_grad_kernel(const float* __restrict__ dy, float* __restrict__ dbias, int n, int out_c,
+                                      int ohw, float beta) {
+    __shared__ float part[256];
+    const int o = blockIdx.x;
+    float s = 0.f;
+    const long long total = (long long)n * ohw;
+    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+        const long long img = i / ohw, sp = i - img * ohw;
+        s += __ldg(dy + (img * out_c + o) * ohw + sp);
+    }
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if ((int)threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dbias[o] = part[0] + (beta != 0.f ? beta * dbias[o] : 0.f);
 }
 
 int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& ma,
@@ -268,7 +336,6 @@ int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& m
 #undef B200_CASE
 }
 
-int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
 struct Plan {
     int bn, bk, split_k, kb_per_split, kblocks, tiles_m, tiles_n;
@@ -830,14 +897,7 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
     if (M == 0) return B200_OK;
     if (x == nullptr || weight == nullptr || y == nullptr) return B200_EINVAL;
     if (M > 0x7fffffffll || K > 0x7fffffffll || n * c * h * w > 0x7fffffffffffll) return B200_ERANGE;
-    // narrowest tile that covers the output channels, as for any narrow product
-    int bn = 32;
-    for (int cand : {256, 128, 64, 32}) {
-        if (cand > 32 && N <= cand / 2) continue;
-        const int64_t tiles = ceil_div(M, kBM) * static_cast<int64_t>(ceil_div(N, cand));
-        bn = cand;
-        if (tiles >= st->sm_count) break;
-    }
+    const int bn = conv_tile_n(*st, M, N);
     GemmParams p{};
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
@@ -878,14 +938,142 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
     p.cv_pad = static_cast<int>(pad);
     p.cv_oh = static_cast<int>(oh);
     p.cv_ow = static_cast<int>(ow);
+    p.cv_oc = static_cast<int>(out_c);
+    p.cv_store_hw = static_cast<int>(oh * ow);
     const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (bn) {
-        case 32: return launch_conv_cfg<32>(p, grid, s);
-        case 64: return launch_conv_cfg<64>(p, grid, s);
-        case 128: return launch_conv_cfg<128>(p, grid, s);
-        default: return launch_conv_cfg<256>(p, grid, s);
+    return launch_conv<1>(bn, p, grid, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200_conv2d_backward_workspace(int64_t n, int64_t c, int64_t h, int64_t w, int64_t out_c, int64_t kh,
+                                      int64_t kw, int64_t stride, int64_t pad) {
+    if (n <= 0 || c <= 0 || out_c <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0) return 0;
+    if (h + 2 * pad < kh || w + 2 * pad < kw) return 0;
+    DeviceState tmp;
+    DeviceState* st = nullptr;
+    if (device_state(&st) != 0) {
+        tmp.sm_count = 148;
+        st = &tmp;
     }
+    const int64_t oh = (h + 2 * pad - kh) / stride + 1, ow = (w + 2 * pad - kw) / stride + 1;
+    return conv_dw_plan(*st, n * oh * ow, out_c, c * kh * kw).bytes;
+}
+
+int b200_conv2d_backward_f32(const float* x, const float* weight, const float* dy, float* dx, float* dweight,
+                             float* dbias, int64_t n, int64_t c, int64_t h, int64_t w, int64_t out_c,
+                             int64_t kh, int64_t kw, int64_t stride, int64_t pad, float beta, int precision,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (n < 0 || c <= 0 || out_c <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0) return B200_EINVAL;
+    if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (h + 2 * pad < kh || w + 2 * pad < kw) return B200_EINVAL;  // empty output
+    const int64_t oh = (h + 2 * pad - kh) / stride + 1, ow = (w + 2 * pad - kw) / stride + 1;
+    const int64_t positions = n * oh * ow, kcols = c * kh * kw, pixels = n * h * w;
+    if (dy == nullptr && positions > 0) return B200_EINVAL;
+    if ((dweight != nullptr && x == nullptr) || (dx != nullptr && weight == nullptr)) return B200_EINVAL;
+    if (positions > 0x7fffffffll || kcols > 0x7fffffffll || pixels > 0x7fffffffll ||
+        out_c * kh * kw > 0x7fffffffll)
+        return B200_ERANGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    GemmParams base{};
+    base.batch = 1;
+    base.n_dest = 1;
+    base.group_m = 16;
+    base.alpha = 1.0f;
+    base.beta = beta;
+    base.precision = precision;
+    base.promote_every = g_opt.promote_every >= 1 ? static_cast<int>(g_opt.promote_every) : 1;
+    base.status = st->status;
+    base.a_lbo = base.b_lbo = 16;
+    base.a_sbo = base.b_sbo = 1024;
+    base.a_kstep = base.b_kstep = 32;
+    base.a_layout = base.b_layout = kLayoutSw128;
+    base.cv_c = static_cast<int>(c);
+    base.cv_h = static_cast<int>(h);
+    base.cv_w = static_cast<int>(w);
+    base.cv_kh = static_cast<int>(kh);
+    base.cv_kw = static_cast<int>(kw);
+    base.cv_stride = static_cast<int>(stride);
+    base.cv_pad = static_cast<int>(pad);
+    base.cv_oh = static_cast<int>(oh);
+    base.cv_ow = static_cast<int>(ow);
+    base.cv_oc = static_cast<int>(out_c);
+
+    if (dbias != nullptr) {
+        conv_bias_grad_kernel<<<static_cast<int>(out_c), 256, 0, s>>>(dy, dbias, static_cast<int>(n),
+                                                                      static_cast<int>(out_c),
+                                                                      static_cast<int>(oh * ow), beta);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
+    }
+    if (dweight != nullptr) {
+        if (positions == 0) {
+            scale_c_kernel<<<st->sm_count * 4, 256, 0, s>>>(dweight, 1, out_c, kcols, kcols, 0, beta);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
+        } else {
+            ConvDwPlan pl = conv_dw_plan(*st, positions, out_c, kcols);
+            const bool ws_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 &&
+                               workspace_bytes >= pl.bytes;
+            if (pl.split_k > 1 && !ws_ok) {  // without room for the partials: one part per tile
+                pl.split_k = 1;
+                pl.kb_per_split = pl.kblocks;
+            }
+            GemmParams p = base;
+            p.M = static_cast<int>(out_c);
+            p.N = static_cast<int>(kcols);
+            p.K = static_cast<int>(positions);
+            p.tiles_m = pl.tiles_m;
+            p.tiles_n = pl.tiles_n;
+            p.kblocks = pl.kblocks;
+            p.split_k = pl.split_k;
+            p.kb_per_split = pl.kb_per_split;
+            p.total_work = pl.tiles_m * pl.tiles_n * pl.split_k;
+            p.A = dy;
+            p.B = x;
+            p.dest[0] = dweight;
+            p.ldc = kcols;
+            p.partial = static_cast<float*>(workspace);
+            p.a_vec_ok = ((reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && ((oh * ow) & 3) == 0) ? 1 : 0;
+            p.c_vec_ok = ((reinterpret_cast<uintptr_t>(dweight) & 15u) == 0 && (kcols & 3) == 0) ? 1 : 0;
+            p.idesc = make_idesc_tf32(kBM, pl.bn, 0, 0);
+            const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+            if ((rc = launch_conv<2>(pl.bn, p, grid, s))) return rc;
+            if (pl.split_k > 1) {
+                const int64_t elems = out_c * kcols;
+                int blocks = static_cast<int>((elems + 255) / 256);
+                if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
+                splitk_reduce_kernel<<<blocks, 256, 0, s>>>(p, static_cast<const float*>(workspace), dweight,
+                                                            pl.split_k, 1, out_c, kcols, kcols, 0, 1.0f, beta);
+                g_launches.fetch_add(1, std::memory_order_relaxed);
+                if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
+            }
+        }
+    }
+    if (dx != nullptr && pixels > 0) {
+        GemmParams p = base;
+        p.M = static_cast<int>(pixels);
+        p.N = static_cast<int>(c);
+        p.K = static_cast<int>(out_c * kh * kw);
+        const int bn = conv_tile_n(*st, pixels, c);
+        p.tiles_m = ceil_div(pixels, kBM);
+        p.tiles_n = ceil_div(c, bn);
+        p.kblocks = ceil_div(static_cast<int64_t>(p.K), 32);
+        p.split_k = 1;
+        p.kb_per_split = p.kblocks;
+        p.total_work = p.tiles_m * p.tiles_n;
+        p.A = dy;
+        p.B = weight;
+        p.dest[0] = dx;
+        p.ldc = c;
+        p.cv_store_hw = static_cast<int>(h * w);
+        p.idesc = make_idesc_tf32(kBM, bn, 0, 0);
+        const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+        if ((rc = launch_conv<3>(bn, p, grid, s))) return rc;
+    }
+    return B200_OK;
 }
 
 }  // extern "C"

@@ -311,6 +311,55 @@ def conv2d(x, weight, bias=None, *, stride: int = 1, padding: int = 0, relu: boo
     return y
 
 
+def conv2d_backward(x, weight, grad_out, *, stride: int = 1, padding: int = 0, need_input_grad: bool = True,
+                    need_weight_grad: bool = True, need_bias_grad: bool = True, accumulate_into=None,
+                    precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """The gradients ``Conv2d`` receives from autograd (src/conv.cpp:280-338 composed with the product's
+    backward, src/tensor_ops.cpp:570-585, and im2col's, src/conv.cpp:236-257), for grad_out (N, outC, oH, oW):
+    ``(grad_x, grad_weight, grad_bias)``, ``None`` where not needed.  No column matrix, no transposes and no
+    col2im scatter are built: one gather kernel per gradient.  ``accumulate_into=(gx, gw, gb)`` adds into
+    existing gradients instead (``Tensor::add_grad``); entries may be ``None``."""
+    import torch
+
+    _check_operand(x, "x")
+    _check_operand(weight, "weight")
+    _check_operand(grad_out, "grad_out")
+    if x.dim() != 4 or weight.dim() != 4 or x.shape[1] != weight.shape[1]:
+        raise ValueError(f"Conv2d gradients need x (N, C, H, W) and weight (outC, C, kH, kW), received "
+                         f"{tuple(x.shape)} and {tuple(weight.shape)}.")
+    if stride < 1 or padding < 0:
+        raise ValueError("Conv2d requires a stride greater than zero and a non-negative padding.")
+    n, c, h, w = x.shape
+    out_c, _, kh, kw = weight.shape
+    if h + 2 * padding < kh or w + 2 * padding < kw:
+        raise ValueError("the window does not fit the padded input")
+    oh, ow = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
+    if list(grad_out.shape) != [n, out_c, oh, ow]:
+        raise ValueError(f"grad_out must be {(n, out_c, oh, ow)}, received {tuple(grad_out.shape)}.")
+    beta = 0.0
+    if accumulate_into is not None:
+        gx, gw, gb = accumulate_into
+        beta = 1.0
+        for name, g, ref in (("grad_x", gx, x), ("grad_weight", gw, weight)):
+            if g is not None:
+                _check_operand(g, name)
+                if g.shape != ref.shape:
+                    raise ValueError(f"{name} must have the shape of its tensor")
+        if gb is not None:
+            _check_operand(gb, "grad_bias")
+            if list(gb.shape) != [out_c]:
+                raise ValueError("grad_bias must have one value per output channel")
+    else:
+        gx = torch.empty_like(x) if need_input_grad else None
+        gw = torch.empty_like(weight) if need_weight_grad else None
+        gb = torch.empty((out_c,), dtype=torch.float32, device=x.device) if need_bias_grad else None
+    dims = dict(n=n, c=c, h=h, w=w, out_c=out_c, kh=kh, kw=kw, stride=stride, pad=padding)
+    ws, ws_bytes = _workspace(x.device, _lib.conv2d_backward_workspace(**dims) if gw is not None else 0)
+    _lib.conv2d_backward(x, weight, grad_out, gx, gw, gb, beta=beta, precision=precision, workspace=ws,
+                         workspace_bytes=ws_bytes, stream=stream, **dims)
+    return gx, gw, gb
+
+
 class Tensor:
     """The slice of ``engine::Tensor`` the matrix-product path needs: a value, an optional
     gradient, ``matmul`` and ``backward`` (include/engine/tensor.hpp:157-198)."""

@@ -23,6 +23,8 @@ EXPORTS = (
     "b200_attention_f32",
     "b200_attention_f32_strided",
     "b200_conv2d_forward_f32",
+    "b200_conv2d_backward_workspace",
+    "b200_conv2d_backward_f32",
     "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
     "b200_matmul_f32",
@@ -79,6 +81,10 @@ def load() -> ctypes.CDLL:
                                                + [c_f, c_int, c_vp])
     lib.b200_conv2d_forward_f32.restype = c_int
     lib.b200_conv2d_forward_f32.argtypes = [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 9 + [c_int, c_int, c_vp]
+    lib.b200_conv2d_backward_workspace.restype = c_sz
+    lib.b200_conv2d_backward_workspace.argtypes = [c_i64] * 9
+    lib.b200_conv2d_backward_f32.restype = c_int
+    lib.b200_conv2d_backward_f32.argtypes = [c_vp] * 6 + [c_i64] * 9 + [c_f, c_int, c_vp, c_sz, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
     lib.b200_gemm_f32_workspace.argtypes = [c_i64, c_i64, c_i64, c_i64]
     lib.b200_matmul_f32.restype = c_int
@@ -185,6 +191,22 @@ def attention_forward_strided(q, k, v, mask, out, weights, *, batch: int, heads:
                                            arr(*v_strides), arr(*out_strides), scale, precision,
                                            _stream_ptr(stream))
     _check(rc, "b200_attention_f32_strided")
+
+
+def conv2d_backward_workspace(*, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int, stride: int = 1,
+                              pad: int = 0) -> int:
+    """Bytes of workspace the weight gradient of this convolution wants."""
+    return int(load().b200_conv2d_backward_workspace(n, c, h, w, out_c, kh, kw, stride, pad))
+
+
+def conv2d_backward(x, weight, dy, dx, dweight, dbias, *, n: int, c: int, h: int, w: int, out_c: int, kh: int,
+                    kw: int, stride: int = 1, pad: int = 0, beta: float = 0.0, precision: int = PRECISION_3XTF32,
+                    workspace=None, workspace_bytes: int = 0, stream=None) -> None:
+    """Gradients of ``conv2d`` (each of dx, dweight, dbias optional): implicit-GEMM kernels, no column matrix."""
+    rc = load().b200_conv2d_backward_f32(_ptr(x), _ptr(weight), _ptr(dy), _ptr(dx), _ptr(dweight), _ptr(dbias), n, c,
+                                         h, w, out_c, kh, kw, stride, pad, beta, precision, _ptr(workspace),
+                                         workspace_bytes, _stream_ptr(stream))
+    _check(rc, "b200_conv2d_backward_f32")
 
 
 def conv2d_forward(x, weight, bias, y, *, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int,

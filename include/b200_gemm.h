@@ -99,6 +99,31 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
                             int64_t kw, int64_t stride, int64_t pad, int relu, int precision,
                             void* stream);
 
+/* The backward pass of Conv2d, without the column matrix, its transpose or col2im's scatter.
+ * The reference derives it through autograd from the forward's pieces (src/conv.cpp:280-338):
+ * the product's backward lambda (src/tensor_ops.cpp:570-585) materialises cols^T and W and runs
+ * two products, im2col's backward scatters dCols with col2im (src/conv.cpp:152-222, 236-257;
+ * its kernel: src/cuda/kernels.cu:428-466), the bias takes the column sums of the gradient.
+ * Here, each optional (pass NULL to skip):
+ *   dweight (out_c, c, kh, kw) = dOut^T x cols  — ONE implicit-GEMM kernel that gathers both operands
+ *           (dy and the im2col view of x) while loading, contracting over the n*oh*ow output
+ *           positions, split over the SMs with a deterministic reduction (second small kernel);
+ *   dx (n, c, h, w)             — ONE gather kernel: dx[n][c][ih][iw] = sum over (o, i, j) of
+ *           dy[n][o][(ih+pad-i)/stride][(iw+pad-j)/stride] * weight[o][c][i][j] (exact divisions
+ *           that land inside dy only), stored in NCHW order;
+ *   dbias (out_c)               — per-channel sums of dy.
+ * beta = 0 overwrites the three gradients, beta = 1 accumulates into them (Tensor::add_grad,
+ * src/tensor.cpp:168-203).  x may be NULL if dweight is, weight may be NULL if dx is.
+ * workspace: b200_conv2d_backward_workspace() bytes, 16-byte aligned, for the weight gradient's
+ * partial sums; without it that kernel runs unsplit (correct, slower). */
+size_t b200_conv2d_backward_workspace(int64_t n, int64_t c, int64_t h, int64_t w, int64_t out_c, int64_t kh,
+                                      int64_t kw, int64_t stride, int64_t pad);
+int b200_conv2d_backward_f32(const float* x, const float* weight, const float* dy, float* dx,
+                             float* dweight, float* dbias, int64_t n, int64_t c, int64_t h, int64_t w,
+                             int64_t out_c, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+                             float beta, int precision, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* scaled_dot_product_attention as ONE kernel (src/transformer.cpp:279-304 composes it from a batched
  * product against a materialised K^T, `* scale`, `+ mask`, Tensor::softmax, src/tensor_ops.cpp:621-647,
  * and a second batched product; its softmax kernels are src/cuda/kernels.cu:835-895):

@@ -154,6 +154,68 @@ def parity_tolerance(K: int) -> float:
     return max(1e-5, 2.0 * K / float(1 << 24))
 
 
+# --- Conv2d as the reference composes it ------------------------------------------------------
+
+def im2col(x: np.ndarray, kh: int, kw: int, stride: int, pad: int):
+    """nn::im2col (src/conv.cpp:61-150): rows (n, oh, ow), columns (c, kh, kw), zeros outside."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
+    xp = np.pad(x, ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    cols = np.empty((n, oh, ow, c, kh, kw), np.float32)
+    for i in range(kh):
+        for j in range(kw):
+            cols[:, :, :, :, i, j] = xp[:, :, i:i + stride * oh:stride, j:j + stride * ow:stride].transpose(0, 2, 3, 1)
+    return cols.reshape(n * oh * ow, c * kh * kw), oh, ow
+
+
+def col2im(cols: np.ndarray, shape, kh: int, kw: int, stride: int, pad: int) -> np.ndarray:
+    """nn::col2im (src/conv.cpp:152-222): every column entry added to the pixel it came from.  The
+    reference walks (oh, ow) ascending, so a pixel receives its terms in descending (kh, kw) order;
+    the loops below add them in that same order (each slice touches a pixel at most once)."""
+    n, c, h, w = shape
+    oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
+    g = _f32(cols).reshape(n, oh, ow, c, kh, kw)
+    out = np.zeros((n, c, h + 2 * pad, w + 2 * pad), np.float32)
+    for i in reversed(range(kh)):
+        for j in reversed(range(kw)):
+            out[:, :, i:i + stride * oh:stride, j:j + stride * ow:stride] += g[:, :, :, :, i, j].transpose(0, 3, 1, 2)
+    return np.ascontiguousarray(out[:, :, pad:pad + h, pad:pad + w])
+
+
+def conv2d_forward(x, weight, bias, stride: int, pad: int) -> np.ndarray:
+    """Conv2d::forward (src/conv.cpp:280-338): im2col, product with the transposed (outC, K) weight
+    view, bias broadcast, (N, spatial, outC) -> (N, outC, oH, oW)."""
+    out_c, _, kh, kw = weight.shape
+    cols, oh, ow = im2col(x, kh, kw, stride, pad)
+    out = matmul(cols, np.ascontiguousarray(_f32(weight).reshape(out_c, -1).T))
+    if bias is not None:
+        out = out + _f32(bias)
+    n = x.shape[0]
+    return np.ascontiguousarray(out.reshape(n, oh * ow, out_c).transpose(0, 2, 1)).reshape(n, out_c, oh, ow)
+
+
+def conv2d_backward(x, weight, grad_out, stride: int, pad: int):
+    """What autograd hands Conv2d's tensors for grad_out (N, outC, oH, oW): the permute's and
+    reshape's backward put the gradient back in (N*spatial, outC) order; the broadcast add sums it
+    over the rows, ascending, for the bias; the product's backward (src/tensor_ops.cpp:570-585)
+    gives dCols = G x W and dW^T = cols^T x G; im2col's backward is col2im (src/conv.cpp:236-257).
+    Returns (grad_x, grad_weight, grad_bias)."""
+    x, weight, grad_out = _f32(x), _f32(weight), _f32(grad_out)
+    n, out_c = grad_out.shape[0], grad_out.shape[1]
+    _, _, kh, kw = weight.shape
+    cols, oh, ow = im2col(x, kh, kw, stride, pad)
+    g = np.ascontiguousarray(grad_out.reshape(n, out_c, oh * ow).transpose(0, 2, 1)).reshape(n * oh * ow, out_c)
+    wt = np.ascontiguousarray(weight.reshape(out_c, -1).T)
+    dcols, dwt = matmul_backward(cols, wt, g)
+    grad_w = np.ascontiguousarray(dwt.T).reshape(weight.shape)
+    grad_b = np.zeros((out_c,), np.float32)
+    for r in range(g.shape[0]):
+        grad_b += g[r]
+    grad_x = col2im(dcols, x.shape, kh, kw, stride, pad)
+    return grad_x, grad_w, grad_b
+
+
 # --- the reference engine itself -------------------------------------------------------------
 
 def ref_matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
@@ -176,3 +238,19 @@ def ref_matmul_time(a: np.ndarray, b: np.ndarray, repeats: int = 1) -> float:
 
 def ref_threads() -> int:
     return int(ref().ref_num_threads())
+
+
+def ref_conv2d_backward(x, weight, bias, grad_out, stride: int, pad: int):
+    """The reference's own Conv2d layer and autograd: (y, grad_x, grad_weight, grad_bias)."""
+    x, weight, grad_out = _f32(x), _f32(weight), _f32(grad_out)
+    n, c, h, w = x.shape
+    out_c, _, kh, kw = weight.shape
+    y = np.empty(grad_out.shape, np.float32)
+    gx, gw, gb = np.empty_like(x), np.empty_like(weight), np.zeros((out_c,), np.float32)
+    b = _f32(bias) if bias is not None else None
+    rc = ref().ref_conv2d_backward(_p(x), _p(weight), _p(b) if b is not None else None, _p(grad_out), _p(y), _p(gx),
+                                   _p(gw), _p(gb), _sz(n), _sz(c), _sz(h), _sz(w), _sz(out_c), _sz(kh), _sz(kw),
+                                   _sz(stride), _sz(pad))
+    if rc != 0:
+        raise ValueError(ref().ref_last_error().decode())
+    return y, gx, gw, (gb if bias is not None else None)

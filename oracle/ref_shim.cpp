@@ -176,4 +176,39 @@ int ref_im2col(const float* x, float* cols, size_t n, size_t c, size_t h, size_t
     }
 }
 
+// Conv2d forward and backward through the engine's own layer and autograd
+// (src/conv.cpp:280-338): y and the three gradients for an explicit grad_output.
+int ref_conv2d_backward(const float* x, const float* weight, const float* bias, const float* grad_out,
+                        float* y, float* grad_x, float* grad_w, float* grad_b, size_t n, size_t c, size_t h,
+                        size_t w, size_t out_c, size_t kh, size_t kw, size_t stride, size_t pad) {
+    try {
+        engine::nn::Conv2d conv(c, out_c, engine::nn::Window2d(kh, kw, stride, pad), bias != nullptr);
+        std::copy_n(weight, conv.weight().size(), conv.weight().data());
+        conv.weight().set_requires_grad(true);
+        conv.weight().zero_grad();
+        if (bias != nullptr) {
+            std::copy_n(bias, out_c, conv.bias().data());
+            conv.bias().set_requires_grad(true);
+            conv.bias().zero_grad();
+        }
+        Tensor X = from_buffer(x, {n, c, h, w}, true);
+        Tensor Y = conv(X);
+        Tensor G = from_buffer(grad_out, Y.shape(), false);
+        Y.backward(G);
+        if (y) std::copy_n(Y.data(), Y.size(), y);
+        Tensor gx = X.grad();
+        Tensor gw = conv.weight().grad();
+        if (grad_x) std::copy_n(gx.data(), gx.size(), grad_x);
+        if (grad_w) std::copy_n(gw.data(), gw.size(), grad_w);
+        if (grad_b && bias != nullptr) {
+            Tensor gb = conv.bias().grad();
+            std::copy_n(gb.data(), gb.size(), grad_b);
+        }
+        return 0;
+    } catch (const std::exception& e) {
+        set_error(e.what());
+        return 1;
+    }
+}
+
 }  // extern "C"

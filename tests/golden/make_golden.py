@@ -7,7 +7,10 @@ Outputs (small, committed):
   pytorch_matmul.npz / .bin   the reference's own PyTorch golden vectors for its matrix product and
                        its gradients (tests/fixtures/matmul*.bin, consumed by
                        tests/test_reference.cpp:99-114), re-encoded as npz.
-  pytorch_conv2d.npz   the reference's PyTorch golden vectors for Conv2d forward (tests/fixtures/conv2d_*.bin).
+  pytorch_conv2d.npz   the reference's PyTorch golden vectors for Conv2d forward and backward
+                       (tests/fixtures/conv2d_*.bin).
+  reference_conv_backward.npz  the UNMODIFIED reference engine's Conv2d forward + autograd backward on
+                       seeded inputs (drawn from its own generator): inputs, output and the three gradients.
   pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward (tests/fixtures/attention*.bin).
   pytorch_multihead.npz  the same for a whole MultiHeadAttention forward (tests/fixtures/multihead_attention.bin).
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
@@ -152,7 +155,7 @@ def main() -> None:
     conv = {}
     for name in ["conv2d_pad1", "conv2d_stride2"]:
         fx = read_fixture(ref_dir / "tests" / "fixtures" / f"{name}.bin")
-        for key in ("input", "weight", "bias", "output"):
+        for key in ("input", "weight", "bias", "output", "grad_output", "grad.input", "grad.weight", "grad.bias"):
             conv[f"{name}/{key}"] = fx[key]
     np.savez(HERE / "pytorch_conv2d.npz", **conv)
 
@@ -171,6 +174,21 @@ def main() -> None:
     #     input, the four projections' weights (in, out) and biases, output
     fx = read_fixture(ref_dir / "tests" / "fixtures" / "multihead_attention.bin")
     np.savez(HERE / "pytorch_multihead.npz", **{k: v for k, v in fx.items() if not k.startswith("grad")})
+
+    # 1e. the reference engine's own Conv2d layer and autograd on seeded inputs
+    cb = {}
+    for tag, (n, c, h, w, oc, k, stride, pad) in {"pad1": (2, 3, 9, 7, 5, 3, 1, 1), "stride2": (3, 2, 11, 8, 4, 3, 2, 0),
+                                                  "k5pad2": (1, 4, 6, 6, 3, 5, 1, 2)}.items():
+        g = RefRng(11)
+        x, wt, b = g.randn((n, c, h, w)), g.rand((oc, c, k, k), -0.5, 0.5), g.rand((oc,), -0.5, 0.5)
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        dy = g.randn((n, oc, oh, ow))
+        y, gx, gw, gb = orc.ref_conv2d_backward(x, wt, b, dy, stride, pad)
+        for key, val in (("x", x), ("weight", wt), ("bias", b), ("grad_output", dy), ("output", y), ("grad.x", gx),
+                         ("grad.weight", gw), ("grad.bias", gb)):
+            cb[f"{tag}/{key}"] = val
+        cb[f"{tag}/window"] = np.array([stride, pad], np.int64)
+    np.savez(HERE / "reference_conv_backward.npz", **cb)
 
     # 2. integer known answers (tests/test_tensor.cpp:47-65, 182-202)
     known = [

@@ -113,3 +113,37 @@ def test_against_reference_build_when_present(orc):
         a, b = g.randn(sa), g.randn(sb)
         a[a < -0.5] = 0.0  # exercise the zero-skip
         assert np.array_equal(orc.matmul(a, b).view(np.uint32), orc.ref_matmul(a, b).view(np.uint32)), (sa, sb)
+
+
+def test_conv_restatement_against_golden(orc, golden_dir):
+    """The numpy restatement of Conv2d forward + backward (im2col, product, bias, permute; product
+    backward, col2im) reproduces, bit for bit, what the unmodified reference engine produced on the
+    recorded seeded inputs, and the reference's PyTorch vectors within their 1e-4."""
+    z = np.load(golden_dir / "reference_conv_backward.npz")
+    for tag in ("pad1", "stride2", "k5pad2"):
+        stride, pad = (int(v) for v in z[f"{tag}/window"])
+        x, wt, b, dy = z[f"{tag}/x"], z[f"{tag}/weight"], z[f"{tag}/bias"], z[f"{tag}/grad_output"]
+        assert np.array_equal(orc.conv2d_forward(x, wt, b, stride, pad), z[f"{tag}/output"])
+        gx, gw, gb = orc.conv2d_backward(x, wt, dy, stride, pad)
+        assert np.array_equal(gx, z[f"{tag}/grad.x"])
+        assert np.array_equal(gw, z[f"{tag}/grad.weight"])
+        assert np.array_equal(gb, z[f"{tag}/grad.bias"])
+    t = np.load(golden_dir / "pytorch_conv2d.npz")
+    for name, stride, pad in [("conv2d_pad1", 1, 1), ("conv2d_stride2", 2, 0)]:
+        gx, gw, gb = orc.conv2d_backward(t[f"{name}/input"], t[f"{name}/weight"], t[f"{name}/grad_output"], stride, pad)
+        assert np.max(np.abs(gx - t[f"{name}/grad.input"])) <= 1e-4
+        assert np.max(np.abs(gw - t[f"{name}/grad.weight"])) <= 1e-4
+        assert np.max(np.abs(gb - t[f"{name}/grad.bias"])) <= 1e-4
+
+
+@pytest.mark.skipif(not __import__("oracle.oracle_py", fromlist=["x"]).have_ref(), reason="reference engine not built here")
+def test_conv_restatement_against_reference_engine(orc):
+    for (n, c, h, w, oc, k, stride, pad) in [(2, 3, 8, 8, 4, 3, 1, 1), (3, 5, 17, 13, 7, 3, 2, 0), (2, 4, 7, 9, 3, 2, 3, 1)]:
+        g = orc.Rng(5)
+        x, wt, b = g.randn((n, c, h, w)), g.randn((oc, c, k, k)), g.randn((oc,))
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        dy = g.randn((n, oc, oh, ow))
+        y, gx, gw, gb = orc.ref_conv2d_backward(x, wt, b, dy, stride, pad)
+        assert np.array_equal(orc.conv2d_forward(x, wt, b, stride, pad), y)
+        gx2, gw2, gb2 = orc.conv2d_backward(x, wt, dy, stride, pad)
+        assert np.array_equal(gx, gx2) and np.array_equal(gw, gw2) and np.array_equal(gb, gb2)
