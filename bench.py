@@ -572,8 +572,9 @@ def run_engine_suite(args):
         w_ = torch.softmax(s_, dim=-1)
         return pkg.matmul(w_.reshape(128, 64, 64), v.reshape(128, 64, 24))
 
-    for label, fn, kernels in () if (args.only and "attention" not in args.only) else (("cfg2 attention core fused (32,4,64,24)", lambda: pkg.scaled_dot_product_attention(q, k, v, mask), 1),
-                               ("cfg2 attention core as 3 kernels (scores+mask, softmax, P.V)", separate, 3)):
+    def time_layer(label, fn, kernels, note="includes the output allocations by the Python wrapper"):
+        if args.only and args.only not in label:
+            return
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
@@ -584,29 +585,46 @@ def run_engine_suite(args):
         torch.cuda.synchronize()
         pkg.status()
         print(json.dumps({"shape": label, "us_per_launch_back_to_back": round(e0.elapsed_time(e1) / 50 * 1e3, 2),
-                          "kernels_per_call": kernels,
-                          "note": "includes the output allocations by the Python wrapper"}), flush=True)
-    # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel
+                          "kernels_per_call": kernels, "note": note}), flush=True)
+
+    time_layer("cfg2 attention core fused (32,4,64,24)", lambda: pkg.scaled_dot_product_attention(q, k, v, mask), 1)
+    time_layer("cfg2 attention core as 3 kernels (scores+mask, softmax, P.V)", separate, 3)
+    # the same core on the (B, S, d_model) projections: heads split and merged by strides, against
+    # the reference's three permute copies in, one out
+    qp, kp, vp = (torch.randn((32, 64, 96), device=dev, generator=gen) for _ in range(3))
+
+    def permuted():
+        q4, k4, v4 = (t.reshape(32, 64, 4, 24).permute(0, 2, 1, 3).contiguous() for t in (qp, kp, vp))
+        o4 = pkg.scaled_dot_product_attention(q4, k4, v4, mask)
+        return o4.permute(0, 2, 1, 3).reshape(32, 64, 96).contiguous()
+
+    time_layer("cfg2 attention, heads by strides (32,64,96)x3 -> (32,64,96)",
+               lambda: pkg.multi_head_attention_core(qp, kp, vp, 4, mask), 1)
+    time_layer("cfg2 attention, heads by permute copies + fused core", permuted, 5)
+    # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel, and
+    # their gradients (product backward over the columns + col2im in the reference)
+    import torch.nn.functional as F
+
     for name, n, c, h, w, out_c, k, stride, pad in CONV_SHAPES:
-        if args.only and args.only not in name:
-            continue
         x = torch.rand((n, c, h, w), device=dev, generator=gen)
         wt = torch.randn((out_c, c, k, k), device=dev, generator=gen)
         b = torch.randn((out_c,), device=dev, generator=gen)
-        for _ in range(5):
-            y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(50):
-            y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
-        e1.record()
-        torch.cuda.synchronize()
-        hot_us = e0.elapsed_time(e1) / 50 * 1e3
-        pkg.status()
-        bytes_alg = 4.0 * (x.numel() + wt.numel() + b.numel() + y.numel())
-        print(json.dumps({"shape": name, "us_per_launch_back_to_back": round(hot_us, 2),
-                          "algorithmic_bytes": int(bytes_alg), "kernels_per_call": 1,
-                          "note": "includes the output allocation by the Python wrapper"}), flush=True)
+        time_layer(name, lambda: pkg.conv2d(x, wt, b, stride=stride, padding=pad), 1)
+        y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
+        dy = torch.randn(y.shape, device=dev, generator=gen)
+
+        def composed_backward():
+            # the reference's sequence with torch's unfold / fold standing in for its im2col / col2im kernels
+            cols = F.unfold(x, k, padding=pad, stride=stride).transpose(1, 2).reshape(-1, c * k * k)
+            g = dy.reshape(n, out_c, -1).transpose(1, 2).reshape(-1, out_c).contiguous()
+            wt_t = wt.reshape(out_c, -1).t().contiguous()   # the (K, outC) operand of the forward product
+            dcols, dwt = pkg.matmul_backward(cols.contiguous(), wt_t, g)
+            dx = F.fold(dcols.reshape(n, -1, c * k * k).transpose(1, 2), (h, w), k, padding=pad, stride=stride)
+            return dx, dwt, g.sum(0)
+
+        time_layer(name.replace("layer", "gradients (dx, dW, db)"),
+                   lambda: pkg.conv2d_backward(x, wt, dy, stride=stride, padding=pad), 3)
+        time_layer(name.replace("layer", "gradients composed: unfold, 2 products, fold, sum"), composed_backward, 8)
 
 
 def run_accuracy_suite(args):

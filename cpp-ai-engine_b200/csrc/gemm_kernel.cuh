@@ -81,6 +81,8 @@ struct GemmParams {
     // stored column matrix, and the output is stored NCHW
     int cv_c, cv_h, cv_w, cv_kh, cv_kw, cv_stride, cv_pad, cv_oh, cv_ow;
     int cv_oc;        // output channels of the convolution (gradient kernels)
+    int cv_table;     // 1: K, the window and the channel count fit the k-decode table (kConvTableMax)
+    int cv_ones_col;  // weight gradient: this column of the column matrix is all ones (bias sums), or -1
     int cv_store_hw;  // pixels per image and channel of the tensor the NCHW store writes
     int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
     int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
@@ -269,8 +271,8 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
 // src/conv.cpp:61-150; zero outside the padded border), split and stored like any A tile.
 // Consecutive threads take consecutive output pixels, which are consecutive input addresses
 // for stride 1.
-__device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int row0, int k0,
-                                                        uint8_t* hi, uint8_t* lo, bool want_lo,
+__device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, const uint32_t* ktab, int row0,
+                                                        int k0, uint8_t* hi, uint8_t* lo, bool want_lo,
                                                         int wtid) {
     constexpr int kUnits = kBM * 8;
     constexpr int kPer = kUnits / kWorkerThreads;
@@ -287,12 +289,23 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
             const int img = gr / ohw, pix = gr - img * ohw;
             const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
             const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
+            uint32_t t4[4] = {0u, 0u, 0u, 0u};
+            if (ktab != nullptr) {
+                const uint4 t = *reinterpret_cast<const uint4*>(ktab + k0 + c * 4);
+                t4[0] = t.x, t4[1] = t.y, t4[2] = t.z, t4[3] = t.w;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gk = k0 + c * 4 + e;
                 if (gk < p.K) {
-                    const int ci = gk / khw, rem = gk - ci * khw;
-                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    int ci, kh, kw;
+                    if (ktab != nullptr) {
+                        ci = t4[e] >> 16, kh = (t4[e] >> 8) & 255, kw = t4[e] & 255;
+                    } else {
+                        ci = gk / khw;
+                        const int rem = gk - ci * khw;
+                        kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    }
                     const int ih = ih0 + kh, iw = iw0 + kw;
                     if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w) {
                         x4[e] = __ldg(p.A + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
@@ -317,6 +330,8 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
         if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
     }
 }
+
+constexpr int kConvTableMax = kWorkerWarps * 4096 / 4;  // entries of the k-decode table
 
 // Stores one unit (4 consecutive k of one tile row) of a K-major swizzled tile, split.
 __device__ __forceinline__ void store_unit_split(uint8_t* hi, uint8_t* lo, bool want_lo, int r, int c,
@@ -390,7 +405,11 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
         const int r = unit >> 3, c = unit & 7;
         const int kc = row0 + r, m0 = k0 + c * 4;
         float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (kc < p.N && m0 < p.K) {
+        if (kc == p.cv_ones_col) {
+            // the bias gradient rides along as one more column of the column matrix: dOut^T x 1
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x4[e] = (m0 + e < p.K) ? 1.0f : 0.0f;
+        } else if (kc < p.N && m0 < p.K) {
             const int ci = kc / khw, rem = kc - ci * khw;
             const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
             int img = m0 / ohw;
@@ -425,8 +444,9 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
 // taken over the terms whose divisions are exact and land inside dy.
 //
 // A tile: row = input pixel m' = (n, ih, iw), k = (o, kh, kw), gathered from dy.
-__device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
-                                                           uint8_t* lo, bool want_lo, int wtid) {
+__device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, const uint32_t* ktab, int row0,
+                                                           int k0, uint8_t* hi, uint8_t* lo, bool want_lo,
+                                                           int wtid) {
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int hw = p.cv_h * p.cv_w, khw = p.cv_kh * p.cv_kw;
     float4 v[kPer];
@@ -439,12 +459,23 @@ __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, 
         if (gr < p.M) {
             const int img = gr / hw, pix = gr - img * hw;
             const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
+            uint32_t t4[4] = {0u, 0u, 0u, 0u};
+            if (ktab != nullptr) {
+                const uint4 t = *reinterpret_cast<const uint4*>(ktab + k0 + c * 4);
+                t4[0] = t.x, t4[1] = t.y, t4[2] = t.z, t4[3] = t.w;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gk = k0 + c * 4 + e;
                 if (gk < p.K) {
-                    const int o = gk / khw, rem = gk - o * khw;
-                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    int o, kh, kw;
+                    if (ktab != nullptr) {
+                        o = t4[e] >> 16, kh = (t4[e] >> 8) & 255, kw = t4[e] & 255;
+                    } else {
+                        o = gk / khw;
+                        const int rem = gk - o * khw;
+                        kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    }
                     int ty = ih + p.cv_pad - kh, tx = iw + p.cv_pad - kw;
                     bool hit = ty >= 0 && tx >= 0;
                     if (p.cv_stride != 1 && hit) {
@@ -738,6 +769,26 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         bool ok = true;
         B200_PROF_DECL;
 
+        // Convolution gathers: k -> (channel, kernel row, kernel column) is the same for every
+        // row of every tile, so it is decoded once per CTA into a table (the NCHW store of these
+        // kernels leaves the epilogue's staging area free) instead of two divisions per element.
+        const uint32_t* ktab = nullptr;
+        if constexpr (kConv == 1 || kConv == 3) {
+            if (p.cv_table) {
+                uint32_t* tab = reinterpret_cast<uint32_t*>(smem + kStages * Cfg::kStageBytes);
+                const int khw = p.cv_kh * p.cv_kw;
+                const int padded = (p.K + 3) & ~3;
+                for (int k = wtid; k < padded; k += kWorkerThreads) {
+                    const int ch = k / khw, rem = k - ch * khw;
+                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                    tab[k] = (static_cast<uint32_t>(ch) << 16) | (static_cast<uint32_t>(kh) << 8) |
+                             static_cast<uint32_t>(kw);
+                }
+                asm volatile("bar.sync 2, %0;" ::"n"(kWorkerThreads) : "memory");
+                ktab = tab;
+            }
+        }
+
         // split_bar / acce_bar are waited on by the MMA lane of the leader CTA only.
         auto arrive_at_leader = [&](uint32_t bar) {
             if constexpr (kPair) {
@@ -837,11 +888,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const float* a_base = p.A + (long long)wk.b * p.strideA;
                     const float* b_base = p.B + (long long)wk.b * p.strideB;
                     if constexpr (kConv == 1) {
-                        conv_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        conv_gather_split_store(p, ktab, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
                     } else if constexpr (kConv == 2) {
                         conv_dy_rows_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
                     } else if constexpr (kConv == 3) {
-                        conv_dx_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        conv_dx_gather_split_store(p, ktab, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
                     } else {
                         ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
                                              p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
@@ -1082,6 +1133,30 @@ __global__ void tail_reduce_kernel(const GemmParams p, int tile_rows, int bn) {
 }
 
 // K == 0: the product is empty, C = beta * C.
+// Sums the weight gradient's split partials (rows x ld_part each, ascending split order within a
+// lane, then a fixed shuffle tree): columns [0, kcols) go to dweight, column kcols — the product with
+// the ones column — to dbias.  One warp per element: the partials of one element are `split`
+// floats a whole matrix apart.
+__global__ void conv_dw_reduce_kernel(const float* __restrict__ partial, int split, int rows, int kcols,
+                                      int ld_part, float* __restrict__ dweight, float* __restrict__ dbias,
+                                      float beta) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const long long total = (long long)rows * ld_part;
+    for (long long i = warp; i < total; i += warps) {
+        float s = 0.f;
+        for (int k = lane; k < split; k += 32) s += partial[(long long)k * total + i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) {
+            const int r = static_cast<int>(i / ld_part), c = static_cast<int>(i - (long long)r * ld_part);
+            float* out = c < kcols ? dweight + (long long)r * kcols + c : dbias + r;
+            *out = s + (beta != 0.f ? beta * *out : 0.f);
+        }
+    }
+}
+
 __global__ void scale_c_kernel(float* __restrict__ C, long long batch, long long M, long long N,
                                long long ldc, long long strideC, float beta) {
     const long long total = batch * M * N;

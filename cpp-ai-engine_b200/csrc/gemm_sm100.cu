@@ -940,6 +940,8 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
     p.cv_ow = static_cast<int>(ow);
     p.cv_oc = static_cast<int>(out_c);
     p.cv_store_hw = static_cast<int>(oh * ow);
+    p.cv_ones_col = -1;
+    p.cv_table = (K <= kConvTableMax && kh < 256 && kw < 256 && c < 65536) ? 1 : 0;
     const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
     return launch_conv<1>(bn, p, grid, static_cast<cudaStream_t>(stream));
 }
@@ -955,7 +957,7 @@ size_t b200_conv2d_backward_workspace(int64_t n, int64_t c, int64_t h, int64_t w
         st = &tmp;
     }
     const int64_t oh = (h + 2 * pad - kh) / stride + 1, ow = (w + 2 * pad - kw) / stride + 1;
-    return conv_dw_plan(*st, n * oh * ow, out_c, c * kh * kw).bytes;
+    return conv_dw_plan(*st, n * oh * ow, out_c, c * kh * kw + 1).bytes;  // + the bias column
 }
 
 int b200_conv2d_backward_f32(const float* x, const float* weight, const float* dy, float* dx, float* dweight,
@@ -1000,30 +1002,20 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
     base.cv_oh = static_cast<int>(oh);
     base.cv_ow = static_cast<int>(ow);
     base.cv_oc = static_cast<int>(out_c);
+    base.cv_ones_col = -1;
 
-    if (dbias != nullptr) {
-        conv_bias_grad_kernel<<<static_cast<int>(out_c), 256, 0, s>>>(dy, dbias, static_cast<int>(n),
-                                                                      static_cast<int>(out_c),
-                                                                      static_cast<int>(oh * ow), beta);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
-    }
-    if (dweight != nullptr) {
-        if (positions == 0) {
-            scale_c_kernel<<<st->sm_count * 4, 256, 0, s>>>(dweight, 1, out_c, kcols, kcols, 0, beta);
-            g_launches.fetch_add(1, std::memory_order_relaxed);
-            if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
-        } else {
-            ConvDwPlan pl = conv_dw_plan(*st, positions, out_c, kcols);
-            const bool ws_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 &&
-                               workspace_bytes >= pl.bytes;
-            if (pl.split_k > 1 && !ws_ok) {  // without room for the partials: one part per tile
-                pl.split_k = 1;
-                pl.kb_per_split = pl.kblocks;
-            }
+    // The bias sums ride along with the weight gradient as one more column (dOut^T x ones) whenever
+    // that product is split; otherwise they have a small kernel of their own.
+    bool bias_done = dbias == nullptr;
+    if (dweight != nullptr && positions > 0) {
+        const int64_t ncols = kcols + (dbias != nullptr ? 1 : 0);
+        ConvDwPlan pl = conv_dw_plan(*st, positions, out_c, ncols);
+        const bool ws_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 &&
+                           workspace_bytes >= pl.bytes;
+        if (pl.split_k > 1 && ws_ok) {
             GemmParams p = base;
             p.M = static_cast<int>(out_c);
-            p.N = static_cast<int>(kcols);
+            p.N = static_cast<int>(ncols);
             p.K = static_cast<int>(positions);
             p.tiles_m = pl.tiles_m;
             p.tiles_n = pl.tiles_n;
@@ -1033,24 +1025,57 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
             p.total_work = pl.tiles_m * pl.tiles_n * pl.split_k;
             p.A = dy;
             p.B = x;
-            p.dest[0] = dweight;
-            p.ldc = kcols;
+            p.dest[0] = dweight;  // not written by a split launch
+            p.ldc = ncols;
             p.partial = static_cast<float*>(workspace);
             p.a_vec_ok = ((reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && ((oh * ow) & 3) == 0) ? 1 : 0;
-            p.c_vec_ok = ((reinterpret_cast<uintptr_t>(dweight) & 15u) == 0 && (kcols & 3) == 0) ? 1 : 0;
+            p.cv_ones_col = dbias != nullptr ? static_cast<int>(kcols) : -1;
             p.idesc = make_idesc_tf32(kBM, pl.bn, 0, 0);
             const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
             if ((rc = launch_conv<2>(pl.bn, p, grid, s))) return rc;
-            if (pl.split_k > 1) {
-                const int64_t elems = out_c * kcols;
-                int blocks = static_cast<int>((elems + 255) / 256);
-                if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
-                splitk_reduce_kernel<<<blocks, 256, 0, s>>>(p, static_cast<const float*>(workspace), dweight,
-                                                            pl.split_k, 1, out_c, kcols, kcols, 0, 1.0f, beta);
-                g_launches.fetch_add(1, std::memory_order_relaxed);
-                if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
-            }
+            const int64_t elems = out_c * ncols;
+            int blocks = static_cast<int>((elems + 7) / 8);  // 8 warps per block, one element per warp
+            if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
+            conv_dw_reduce_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(workspace), pl.split_k,
+                                                         static_cast<int>(out_c), static_cast<int>(kcols),
+                                                         static_cast<int>(ncols), dweight, dbias, beta);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
+            bias_done = true;
+        } else {  // a single part per tile, stored directly
+            ConvDwPlan one = conv_dw_plan(*st, positions, out_c, kcols);
+            GemmParams p = base;
+            p.M = static_cast<int>(out_c);
+            p.N = static_cast<int>(kcols);
+            p.K = static_cast<int>(positions);
+            p.tiles_m = one.tiles_m;
+            p.tiles_n = one.tiles_n;
+            p.kblocks = one.kblocks;
+            p.split_k = 1;
+            p.kb_per_split = one.kblocks;
+            p.total_work = one.tiles_m * one.tiles_n;
+            p.A = dy;
+            p.B = x;
+            p.dest[0] = dweight;
+            p.ldc = kcols;
+            p.a_vec_ok = ((reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && ((oh * ow) & 3) == 0) ? 1 : 0;
+            p.c_vec_ok = ((reinterpret_cast<uintptr_t>(dweight) & 15u) == 0 && (kcols & 3) == 0) ? 1 : 0;
+            p.cv_ones_col = -1;
+            p.idesc = make_idesc_tf32(kBM, one.bn, 0, 0);
+            const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+            if ((rc = launch_conv<2>(one.bn, p, grid, s))) return rc;
         }
+    } else if (dweight != nullptr && positions == 0) {
+        scale_c_kernel<<<st->sm_count * 4, 256, 0, s>>>(dweight, 1, out_c, kcols, kcols, 0, beta);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
+    }
+    if (!bias_done) {
+        conv_bias_grad_kernel<<<static_cast<int>(out_c), 256, 0, s>>>(dy, dbias, static_cast<int>(n),
+                                                                      static_cast<int>(out_c),
+                                                                      static_cast<int>(oh * ow), beta);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if ((rc = static_cast<int>(cudaGetLastError()))) return rc;
     }
     if (dx != nullptr && pixels > 0) {
         GemmParams p = base;
@@ -1069,6 +1094,7 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
         p.dest[0] = dx;
         p.ldc = c;
         p.cv_store_hw = static_cast<int>(h * w);
+        p.cv_table = (p.K <= kConvTableMax && kh < 256 && kw < 256 && out_c < 65536) ? 1 : 0;
         p.idesc = make_idesc_tf32(kBM, bn, 0, 0);
         const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
         if ((rc = launch_conv<3>(bn, p, grid, s))) return rc;
