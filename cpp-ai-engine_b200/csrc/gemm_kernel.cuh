@@ -81,7 +81,7 @@ struct GemmParams {
     // stored column matrix, and the output is stored NCHW
     int cv_c, cv_h, cv_w, cv_kh, cv_kw, cv_stride, cv_pad, cv_oh, cv_ow;
     int cv_oc;        // output channels of the convolution (gradient kernels)
-    int cv_table;     // 1: K, the window and the channel count fit the k-decode table (kConvTableMax)
+    int cv_table;     // 1: the gather runs from the per-CTA k tables (K <= kConvTableMax, offsets fit 32 bits)
     int cv_ones_col;  // weight gradient: this column of the column matrix is all ones (bias sums), or -1
     int cv_store_hw;  // pixels per image and channel of the tensor the NCHW store writes
     int tile_offset;    // first tile of this launch (tail-wave launches start past the full waves)
@@ -271,8 +271,8 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
 // src/conv.cpp:61-150; zero outside the padded border), split and stored like any A tile.
 // Consecutive threads take consecutive output pixels, which are consecutive input addresses
 // for stride 1.
-__device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, const uint32_t* ktab, int row0,
-                                                        int k0, uint8_t* hi, uint8_t* lo, bool want_lo,
+__device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int row0, int k0,
+                                                        uint8_t* hi, uint8_t* lo, bool want_lo,
                                                         int wtid) {
     constexpr int kUnits = kBM * 8;
     constexpr int kPer = kUnits / kWorkerThreads;
@@ -289,23 +289,12 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, con
             const int img = gr / ohw, pix = gr - img * ohw;
             const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
             const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
-            uint32_t t4[4] = {0u, 0u, 0u, 0u};
-            if (ktab != nullptr) {
-                const uint4 t = *reinterpret_cast<const uint4*>(ktab + k0 + c * 4);
-                t4[0] = t.x, t4[1] = t.y, t4[2] = t.z, t4[3] = t.w;
-            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gk = k0 + c * 4 + e;
                 if (gk < p.K) {
-                    int ci, kh, kw;
-                    if (ktab != nullptr) {
-                        ci = t4[e] >> 16, kh = (t4[e] >> 8) & 255, kw = t4[e] & 255;
-                    } else {
-                        ci = gk / khw;
-                        const int rem = gk - ci * khw;
-                        kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-                    }
+                    const int ci = gk / khw, rem = gk - ci * khw;
+                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
                     const int ih = ih0 + kh, iw = iw0 + kw;
                     if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w) {
                         x4[e] = __ldg(p.A + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
@@ -331,8 +320,6 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, con
     }
 }
 
-constexpr int kConvTableMax = kWorkerWarps * 4096 / 4;  // entries of the k-decode table
-
 // Stores one unit (4 consecutive k of one tile row) of a K-major swizzled tile, split.
 __device__ __forceinline__ void store_unit_split(uint8_t* hi, uint8_t* lo, bool want_lo, int r, int c,
                                                  const float4& v) {
@@ -345,6 +332,58 @@ __device__ __forceinline__ void store_unit_split(uint8_t* hi, uint8_t* lo, bool 
     *reinterpret_cast<float4*>(hi + off) = h;
     if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
 }
+
+// Table-driven gather of a convolution's A tile (forward: from x; input gradient with stride 1:
+// from dy).  Element (row, k) of the tile is  src[row.base + koff[k]]  when
+// 0 <= row.y + dy[k] < ymax and 0 <= row.x + dx[k] < xmax, else zero, where
+//   forward:         row = (n, oh, ow):  base = n*C*H*W + y*W + x,  (y, x) = (oh*s - pad, ow*s - pad);
+//                    k = (c, kh, kw):    koff = c*H*W + kh*W + kw,  (dy, dx) = (kh, kw);  limits (H, W)
+//   input gradient:  row = (n, ih, iw):  base = n*O*oH*oW + y*oW + x,  (y, x) = (ih + pad, iw + pad);
+//                    k = (o, kh, kw):    koff = o*oH*oW - kh*oW - kw,  (dy, dx) = (-kh, -kw);  limits (oH, oW).
+// The k side is the same for every row of every tile: each CTA writes it once into two tables in
+// the epilogue's staging area (these kernels store NCHW straight from registers and leave it
+// free); the row side is computed once per tile.  What is left per element is two adds and two
+// unsigned compares instead of four divisions.
+constexpr int kConvTableMax = kWorkerWarps * 4096 / 8;  // k values the two tables hold
+constexpr int kConvDeltaBias = 32768;                   // (dy, dx) are stored + bias in 16 bits each
+
+struct ConvRow {
+    long long base;
+    int y, x;  // already minus kConvDeltaBias; a row past M gets a y that fails every compare
+};
+
+__device__ __forceinline__ void conv_table_gather_split_store(const float* __restrict__ src, const int* koff,
+                                                              const uint32_t* kdelta, const ConvRow& row,
+                                                              uint32_t ymax, uint32_t xmax, int k0, int K,
+                                                              uint8_t* hi, uint8_t* lo, bool want_lo, int wtid) {
+    constexpr int kPer = kBM * 8 / kWorkerThreads;
+    static_assert(kWorkerThreads % kBM == 0, "a worker keeps one tile row");
+    const int r = wtid % kBM;
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int c = wtid / kBM + u * (kWorkerThreads / kBM);
+        const int gk = k0 + c * 4;
+        float x4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (gk < K) {  // the tables are padded to a multiple of 4 with entries that fail the compares
+            const int4 ko = *reinterpret_cast<const int4*>(koff + gk);
+            const uint4 kd = *reinterpret_cast<const uint4*>(kdelta + gk);
+            const int ko4[4] = {ko.x, ko.y, ko.z, ko.w};
+            const uint32_t kd4[4] = {kd.x, kd.y, kd.z, kd.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t ty = static_cast<uint32_t>(row.y + static_cast<int>(kd4[e] >> 16));
+                const uint32_t tx = static_cast<uint32_t>(row.x + static_cast<int>(kd4[e] & 0xffffu));
+                if (ty < ymax && tx < xmax) x4[e] = __ldg(src + row.base + ko4[e]);
+            }
+        }
+        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u)
+        store_unit_split(hi, lo, want_lo, r, wtid / kBM + u * (kWorkerThreads / kBM), v[u]);
+}
+
 
 // Weight gradient of a convolution, dW (outC x C*kH*kW) = dOut^T x cols, with neither dOut^T nor
 // cols ever written (the reference's backward of `cols.matmul(W^T)`, src/tensor_ops.cpp:570-585,
@@ -444,9 +483,8 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
 // taken over the terms whose divisions are exact and land inside dy.
 //
 // A tile: row = input pixel m' = (n, ih, iw), k = (o, kh, kw), gathered from dy.
-__device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, const uint32_t* ktab, int row0,
-                                                           int k0, uint8_t* hi, uint8_t* lo, bool want_lo,
-                                                           int wtid) {
+__device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
+                                                           uint8_t* lo, bool want_lo, int wtid) {
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int hw = p.cv_h * p.cv_w, khw = p.cv_kh * p.cv_kw;
     float4 v[kPer];
@@ -459,23 +497,12 @@ __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, 
         if (gr < p.M) {
             const int img = gr / hw, pix = gr - img * hw;
             const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
-            uint32_t t4[4] = {0u, 0u, 0u, 0u};
-            if (ktab != nullptr) {
-                const uint4 t = *reinterpret_cast<const uint4*>(ktab + k0 + c * 4);
-                t4[0] = t.x, t4[1] = t.y, t4[2] = t.z, t4[3] = t.w;
-            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gk = k0 + c * 4 + e;
                 if (gk < p.K) {
-                    int o, kh, kw;
-                    if (ktab != nullptr) {
-                        o = t4[e] >> 16, kh = (t4[e] >> 8) & 255, kw = t4[e] & 255;
-                    } else {
-                        o = gk / khw;
-                        const int rem = gk - o * khw;
-                        kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-                    }
+                    const int o = gk / khw, rem = gk - o * khw;
+                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
                     int ty = ih + p.cv_pad - kh, tx = iw + p.cv_pad - kw;
                     bool hit = ty >= 0 && tx >= 0;
                     if (p.cv_stride != 1 && hit) {
@@ -769,23 +796,35 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         bool ok = true;
         B200_PROF_DECL;
 
-        // Convolution gathers: k -> (channel, kernel row, kernel column) is the same for every
-        // row of every tile, so it is decoded once per CTA into a table (the NCHW store of these
-        // kernels leaves the epilogue's staging area free) instead of two divisions per element.
-        const uint32_t* ktab = nullptr;
+        // Convolution gathers: the k side of the addressing, once per CTA (see
+        // conv_table_gather_split_store).
+        const int* koff = nullptr;
+        const uint32_t* kdelta = nullptr;
         if constexpr (kConv == 1 || kConv == 3) {
             if (p.cv_table) {
-                uint32_t* tab = reinterpret_cast<uint32_t*>(smem + kStages * Cfg::kStageBytes);
+                int* t_off = reinterpret_cast<int*>(smem + kStages * Cfg::kStageBytes);
+                uint32_t* t_del = reinterpret_cast<uint32_t*>(t_off + kConvTableMax);
                 const int khw = p.cv_kh * p.cv_kw;
                 const int padded = (p.K + 3) & ~3;
                 for (int k = wtid; k < padded; k += kWorkerThreads) {
                     const int ch = k / khw, rem = k - ch * khw;
                     const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-                    tab[k] = (static_cast<uint32_t>(ch) << 16) | (static_cast<uint32_t>(kh) << 8) |
-                             static_cast<uint32_t>(kw);
+                    if (k >= p.K) {
+                        t_off[k] = 0;
+                        t_del[k] = 0;  // delta -32768: no row passes the compare
+                    } else if constexpr (kConv == 1) {
+                        t_off[k] = (ch * p.cv_h + kh) * p.cv_w + kw;
+                        t_del[k] = (static_cast<uint32_t>(kConvDeltaBias + kh) << 16) |
+                                   static_cast<uint32_t>(kConvDeltaBias + kw);
+                    } else {
+                        t_off[k] = (ch * p.cv_oh - kh) * p.cv_ow - kw;
+                        t_del[k] = (static_cast<uint32_t>(kConvDeltaBias - kh) << 16) |
+                                   static_cast<uint32_t>(kConvDeltaBias - kw);
+                    }
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(kWorkerThreads) : "memory");
-                ktab = tab;
+                koff = t_off;
+                kdelta = t_del;
             }
         }
 
@@ -842,6 +881,32 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             const int nkb = wk.kb1 - wk.kb0;
 #pragma unroll
             for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+            ConvRow crow{0, 0, 0};
+            if constexpr (kConv == 1 || kConv == 3) {
+                if (koff != nullptr) {
+                    const int gr = wk.mt * kBM + wtid % kBM;
+                    if (gr >= p.M) {
+                        crow.y = -2 * kConvDeltaBias - (1 << 20);  // fails every compare
+                        crow.x = 0;
+                    } else if constexpr (kConv == 1) {
+                        const int ohw = p.cv_oh * p.cv_ow;
+                        const int img = gr / ohw, pix = gr - img * ohw;
+                        const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
+                        const int y = oh * p.cv_stride - p.cv_pad, x = ow * p.cv_stride - p.cv_pad;
+                        crow.base = ((long long)img * p.cv_c * p.cv_h + y) * p.cv_w + x;
+                        crow.y = y - kConvDeltaBias;
+                        crow.x = x - kConvDeltaBias;
+                    } else {
+                        const int hw = p.cv_h * p.cv_w;
+                        const int img = gr / hw, pix = gr - img * hw;
+                        const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
+                        const int y = ih + p.cv_pad, x = iw + p.cv_pad;
+                        crow.base = ((long long)img * p.cv_oc * p.cv_oh + y) * p.cv_ow + x;
+                        crow.y = y - kConvDeltaBias;
+                        crow.x = x - kConvDeltaBias;
+                    }
+                }
+            }
 
             for (int i = 0; i < nkb && ok; ++i, ++it) {
                 const uint32_t s = it % kStages;
@@ -877,22 +942,38 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                     B200_T1(6);
                 } else {
-                    bool got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
-                                        kStatWorkerFull);
-                    got = __all_sync(0xffffffffu, got);
+                    bool got;
+                    {
+                        B200_T0();
+                        got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
+                                       kStatWorkerFull);
+                        got = __all_sync(0xffffffffu, got);
+                        B200_T1(5);
+                    }
                     if (!got) {
                         ok = false;
                         break;
                     }
+                    B200_T0();
                     const int k0 = (wk.kb0 + i) * BK;
                     const float* a_base = p.A + (long long)wk.b * p.strideA;
                     const float* b_base = p.B + (long long)wk.b * p.strideB;
                     if constexpr (kConv == 1) {
-                        conv_gather_split_store(p, ktab, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        if (koff != nullptr) {
+                            conv_table_gather_split_store(p.A, koff, kdelta, crow, p.cv_h, p.cv_w, k0, p.K, stage,
+                                                          stage + Cfg::kHalf, prec3, wtid);
+                        } else {
+                            conv_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        }
                     } else if constexpr (kConv == 2) {
                         conv_dy_rows_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
                     } else if constexpr (kConv == 3) {
-                        conv_dx_gather_split_store(p, ktab, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        if (koff != nullptr) {
+                            conv_table_gather_split_store(p.A, koff, kdelta, crow, p.cv_oh, p.cv_ow, k0, p.K, stage,
+                                                          stage + Cfg::kHalf, prec3, wtid);
+                        } else {
+                            conv_dx_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
+                        }
                     } else {
                         ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
                                              p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
@@ -908,6 +989,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                                             p.N, k0, p.K, stage + Cfg::kABytes,
                                             stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
                     }
+                    B200_T1(6);
                 }
                 // generic-proxy writes -> visible to the tensor core's async-proxy reads
                 fence_proxy_async_smem();
@@ -932,6 +1014,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             ++chain;
 
             // ---------------------------------------------------------------- epilogue
+            B200_T0();
             // A thread holds kCols consecutive columns of ONE row; stored as it stands, every
             // store instruction of a warp would touch 32 different rows with 16 bytes each.
             // Each warp therefore turns 32 x 32 blocks through its own 4 KB of shared memory
@@ -1053,6 +1136,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
+            B200_T1(9);
         }
         B200_PROF_FLUSH(wtid == 0);
     }

@@ -941,7 +941,10 @@ int b200_conv2d_forward_f32(const float* x, const float* weight, const float* bi
     p.cv_oc = static_cast<int>(out_c);
     p.cv_store_hw = static_cast<int>(oh * ow);
     p.cv_ones_col = -1;
-    p.cv_table = (K <= kConvTableMax && kh < 256 && kw < 256 && c < 65536) ? 1 : 0;
+    p.cv_table = (K <= kConvTableMax && kh < 16384 && kw < 16384 && h + 2 * pad < 16384 && w + 2 * pad < 16384 &&
+                  c * h * w < 0x7fffffffll)
+                     ? 1
+                     : 0;
     const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
     return launch_conv<1>(bn, p, grid, static_cast<cudaStream_t>(stream));
 }
@@ -1003,6 +1006,9 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
     base.cv_ow = static_cast<int>(ow);
     base.cv_oc = static_cast<int>(out_c);
     base.cv_ones_col = -1;
+#ifdef B200_PHASE_PROFILE
+    base.prof = g_prof;
+#endif
 
     // The bias sums ride along with the weight gradient as one more column (dOut^T x ones) whenever
     // that product is split; otherwise they have a small kernel of their own.
@@ -1094,7 +1100,10 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
         p.dest[0] = dx;
         p.ldc = c;
         p.cv_store_hw = static_cast<int>(h * w);
-        p.cv_table = (p.K <= kConvTableMax && kh < 256 && kw < 256 && out_c < 65536) ? 1 : 0;
+        p.cv_table = (stride == 1 && p.K <= kConvTableMax && kh < 16384 && kw < 16384 && h + 2 * pad < 16384 &&
+                      w + 2 * pad < 16384 && out_c * oh * ow < 0x7fffffffll)
+                         ? 1
+                         : 0;
         p.idesc = make_idesc_tf32(kBM, bn, 0, 0);
         const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
         if ((rc = launch_conv<3>(bn, p, grid, s))) return rc;
