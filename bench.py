@@ -613,18 +613,32 @@ def run_engine_suite(args):
         y = pkg.conv2d(x, wt, b, stride=stride, padding=pad)
         dy = torch.randn(y.shape, device=dev, generator=gen)
 
+        # The reference's sequence — im2col, product backward (two products), col2im, column sums —
+        # with one index gather / one index scatter-add standing in for its im2col / col2im kernels.
+        oh, ow = y.shape[2], y.shape[3]
+        hp, wp = h + 2 * pad, w + 2 * pad
+        ar = torch.arange
+        row_base = ((ar(n, device=dev).view(n, 1, 1) * c * hp + ar(oh, device=dev).view(1, oh, 1) * stride) * wp
+                    + ar(ow, device=dev).view(1, 1, ow) * stride).reshape(-1, 1)
+        col_off = ((ar(c, device=dev).view(c, 1, 1) * hp + ar(k, device=dev).view(1, k, 1)) * wp
+                   + ar(k, device=dev).view(1, 1, k)).reshape(1, -1)
+        gather_idx = (row_base + col_off).reshape(-1)
+
         def composed_backward():
-            # the reference's sequence with torch's unfold / fold standing in for its im2col / col2im kernels
-            cols = F.unfold(x, k, padding=pad, stride=stride).transpose(1, 2).reshape(-1, c * k * k)
+            xp = F.pad(x, (pad, pad, pad, pad))
+            cols = xp.reshape(-1)[gather_idx].reshape(n * oh * ow, c * k * k)
             g = dy.reshape(n, out_c, -1).transpose(1, 2).reshape(-1, out_c).contiguous()
             wt_t = wt.reshape(out_c, -1).t().contiguous()   # the (K, outC) operand of the forward product
-            dcols, dwt = pkg.matmul_backward(cols.contiguous(), wt_t, g)
-            dx = F.fold(dcols.reshape(n, -1, c * k * k).transpose(1, 2), (h, w), k, padding=pad, stride=stride)
+            dcols, dwt = pkg.matmul_backward(cols, wt_t, g)
+            dxp = torch.zeros(n * c * hp * wp, device=dev)
+            dxp.index_add_(0, gather_idx, dcols.reshape(-1))
+            dx = dxp.reshape(n, c, hp, wp)[:, :, pad:pad + h, pad:pad + w].contiguous()
             return dx, dwt, g.sum(0)
 
         time_layer(name.replace("layer", "gradients (dx, dW, db)"),
                    lambda: pkg.conv2d_backward(x, wt, dy, stride=stride, padding=pad), 3)
-        time_layer(name.replace("layer", "gradients composed: unfold, 2 products, fold, sum"), composed_backward, 8)
+        time_layer(name.replace("layer", "gradients composed: im2col gather, 2 products, col2im scatter, sums"),
+                   composed_backward, 11)
 
 
 def run_accuracy_suite(args):

@@ -42,6 +42,8 @@
 // through to the common exit where TMEM is released.
 #pragma once
 
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 
 namespace b200 {
@@ -198,71 +200,74 @@ __device__ __forceinline__ float finish_output(const GemmParams& p, float scaled
 // Loads a ROWS x 32 tile of one operand with plain global loads, splits it and stores the
 // head / tail tiles in the K-major 128-byte-swizzled layout.  `k_contig`: k is the contiguous
 // index of the stored matrix (A not transposed, B transposed).
-template <int ROWS>
+template <int ROWS, bool kLoad, bool kStore>
 __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, long long ld,
                                                 bool k_contig, bool vec_ok, int row0, int row_max,
                                                 int k0, int K, uint8_t* hi, uint8_t* lo,
-                                                bool want_lo, int wtid) {
+                                                bool want_lo, int wtid, float4* v) {
     constexpr int kChunks = 8;  // 16-byte chunks per 128-byte row
     constexpr int kUnits = ROWS * kChunks;
     constexpr int kPer = kUnits / kWorkerThreads;
     static_assert(kUnits % kWorkerThreads == 0, "tile does not divide over the workers");
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        int r, c;
-        if (k_contig) {
-            r = unit / kChunks;
-            c = unit % kChunks;
-        } else {
-            r = unit % ROWS;
-            c = unit / ROWS;
-        }
-        const int gr = row0 + r;
-        const int gk = k0 + c * 4;
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gr < row_max && gk < K) {
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            int r, c;
             if (k_contig) {
-                const float* src = base + (long long)gr * ld + gk;
-                if (vec_ok && gk + 3 < K) {
-                    x = __ldg(reinterpret_cast<const float4*>(src));
-                } else {
-                    x.x = __ldg(src);
-                    if (gk + 1 < K) x.y = __ldg(src + 1);
-                    if (gk + 2 < K) x.z = __ldg(src + 2);
-                    if (gk + 3 < K) x.w = __ldg(src + 3);
-                }
+                r = unit / kChunks;
+                c = unit % kChunks;
             } else {
-                const float* src = base + (long long)gk * ld + gr;
-                x.x = __ldg(src);
-                if (gk + 1 < K) x.y = __ldg(src + ld);
-                if (gk + 2 < K) x.z = __ldg(src + 2 * ld);
-                if (gk + 3 < K) x.w = __ldg(src + 3 * ld);
+                r = unit % ROWS;
+                c = unit / ROWS;
             }
+            const int gr = row0 + r;
+            const int gk = k0 + c * 4;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gr < row_max && gk < K) {
+                if (k_contig) {
+                    const float* src = base + (long long)gr * ld + gk;
+                    if (vec_ok && gk + 3 < K) {
+                        x = __ldg(reinterpret_cast<const float4*>(src));
+                    } else {
+                        x.x = __ldg(src);
+                        if (gk + 1 < K) x.y = __ldg(src + 1);
+                        if (gk + 2 < K) x.z = __ldg(src + 2);
+                        if (gk + 3 < K) x.w = __ldg(src + 3);
+                    }
+                } else {
+                    const float* src = base + (long long)gk * ld + gr;
+                    x.x = __ldg(src);
+                    if (gk + 1 < K) x.y = __ldg(src + ld);
+                    if (gk + 2 < K) x.z = __ldg(src + 2 * ld);
+                    if (gk + 3 < K) x.w = __ldg(src + 3 * ld);
+                }
+            }
+            v[u] = x;
         }
-        v[u] = x;
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        int r, c;
-        if (k_contig) {
-            r = unit / kChunks;
-            c = unit % kChunks;
-        } else {
-            r = unit % ROWS;
-            c = unit / ROWS;
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            int r, c;
+            if (k_contig) {
+                r = unit / kChunks;
+                c = unit % kChunks;
+            } else {
+                r = unit % ROWS;
+                c = unit / ROWS;
+            }
+            const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
+                                 (uint32_t)((c ^ (r & 7)) << 4);
+            float4 h, l;
+            tf32_split(v[u].x, h.x, l.x);
+            tf32_split(v[u].y, h.y, l.y);
+            tf32_split(v[u].z, h.z, l.z);
+            tf32_split(v[u].w, h.w, l.w);
+            *reinterpret_cast<float4*>(hi + off) = h;
+            if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
         }
-        const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
-                             (uint32_t)((c ^ (r & 7)) << 4);
-        float4 h, l;
-        tf32_split(v[u].x, h.x, l.x);
-        tf32_split(v[u].y, h.y, l.y);
-        tf32_split(v[u].z, h.z, l.z);
-        tf32_split(v[u].w, h.w, l.w);
-        *reinterpret_cast<float4*>(hi + off) = h;
-        if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
     }
 }
 
@@ -271,52 +276,56 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
 // src/conv.cpp:61-150; zero outside the padded border), split and stored like any A tile.
 // Consecutive threads take consecutive output pixels, which are consecutive input addresses
 // for stride 1.
+template <bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int row0, int k0,
                                                         uint8_t* hi, uint8_t* lo, bool want_lo,
-                                                        int wtid) {
+                                                        int wtid, float4* v) {
     constexpr int kUnits = kBM * 8;
     constexpr int kPer = kUnits / kWorkerThreads;
     const int ohw = p.cv_oh * p.cv_ow;
     const int khw = p.cv_kh * p.cv_kw;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit % kBM, c = unit / kBM;
-        const int gr = row0 + r;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (gr < p.M) {
-            const int img = gr / ohw, pix = gr - img * ohw;
-            const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
-            const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int gk = k0 + c * 4 + e;
-                if (gk < p.K) {
-                    const int ci = gk / khw, rem = gk - ci * khw;
-                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-                    const int ih = ih0 + kh, iw = iw0 + kw;
-                    if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w) {
-                        x4[e] = __ldg(p.A + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit % kBM, c = unit / kBM;
+            const int gr = row0 + r;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gr < p.M) {
+                const int img = gr / ohw, pix = gr - img * ohw;
+                const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
+                const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
+    #pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int gk = k0 + c * 4 + e;
+                    if (gk < p.K) {
+                        const int ci = gk / khw, rem = gk - ci * khw;
+                        const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                        const int ih = ih0 + kh, iw = iw0 + kw;
+                        if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w) {
+                            x4[e] = __ldg(p.A + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
+                        }
                     }
                 }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit % kBM, c = unit / kBM;
-        const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
-                             (uint32_t)((c ^ (r & 7)) << 4);
-        float4 h, l;
-        tf32_split(v[u].x, h.x, l.x);
-        tf32_split(v[u].y, h.y, l.y);
-        tf32_split(v[u].z, h.z, l.z);
-        tf32_split(v[u].w, h.w, l.w);
-        *reinterpret_cast<float4*>(hi + off) = h;
-        if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit % kBM, c = unit / kBM;
+            const uint32_t off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u +
+                                 (uint32_t)((c ^ (r & 7)) << 4);
+            float4 h, l;
+            tf32_split(v[u].x, h.x, l.x);
+            tf32_split(v[u].y, h.y, l.y);
+            tf32_split(v[u].z, h.z, l.z);
+            tf32_split(v[u].w, h.w, l.w);
+            *reinterpret_cast<float4*>(hi + off) = h;
+            if (want_lo) *reinterpret_cast<float4*>(lo + off) = l;
+        }
     }
 }
 
@@ -352,36 +361,42 @@ struct ConvRow {
     int y, x;  // already minus kConvDeltaBias; a row past M gets a y that fails every compare
 };
 
+template <bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_table_gather_split_store(const float* __restrict__ src, const int* koff,
                                                               const uint32_t* kdelta, const ConvRow& row,
                                                               uint32_t ymax, uint32_t xmax, int k0, int K,
-                                                              uint8_t* hi, uint8_t* lo, bool want_lo, int wtid) {
+                                                              uint8_t* hi, uint8_t* lo, bool want_lo, int wtid,
+                                                              float4* v) {
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     static_assert(kWorkerThreads % kBM == 0, "a worker keeps one tile row");
     const int r = wtid % kBM;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int c = wtid / kBM + u * (kWorkerThreads / kBM);
-        const int gk = k0 + c * 4;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (gk < K) {  // the tables are padded to a multiple of 4 with entries that fail the compares
-            const int4 ko = *reinterpret_cast<const int4*>(koff + gk);
-            const uint4 kd = *reinterpret_cast<const uint4*>(kdelta + gk);
-            const int ko4[4] = {ko.x, ko.y, ko.z, ko.w};
-            const uint32_t kd4[4] = {kd.x, kd.y, kd.z, kd.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t ty = static_cast<uint32_t>(row.y + static_cast<int>(kd4[e] >> 16));
-                const uint32_t tx = static_cast<uint32_t>(row.x + static_cast<int>(kd4[e] & 0xffffu));
-                if (ty < ymax && tx < xmax) x4[e] = __ldg(src + row.base + ko4[e]);
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int c = wtid / kBM + u * (kWorkerThreads / kBM);
+            const int gk = k0 + c * 4;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gk < K) {  // the tables are padded to a multiple of 4 with entries that fail the compares
+                const int4 ko = *reinterpret_cast<const int4*>(koff + gk);
+                const uint4 kd = *reinterpret_cast<const uint4*>(kdelta + gk);
+                const int ko4[4] = {ko.x, ko.y, ko.z, ko.w};
+                const uint32_t kd4[4] = {kd.x, kd.y, kd.z, kd.w};
+    #pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t ty = static_cast<uint32_t>(row.y + static_cast<int>(kd4[e] >> 16));
+                    const uint32_t tx = static_cast<uint32_t>(row.x + static_cast<int>(kd4[e] & 0xffffu));
+                    if (ty < ymax && tx < xmax) x4[e] = __ldg(src + row.base + ko4[e]);
+                }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u)
-        store_unit_split(hi, lo, want_lo, r, wtid / kBM + u * (kWorkerThreads / kBM), v[u]);
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            store_unit_split(hi, lo, want_lo, r, wtid / kBM + u * (kWorkerThreads / kBM), v[u]);
+        }
+    }
 }
 
 
@@ -393,87 +408,94 @@ __device__ __forceinline__ void conv_table_gather_split_store(const float* __res
 // A tile: row = output channel o, k = m, read from dy (N, outC, oH, oW): for one channel,
 // consecutive m of an image are consecutive floats.  Rows past outC are left as they are: they
 // feed accumulator rows that are never stored.
+template <bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_dy_rows_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
-                                                         uint8_t* lo, bool want_lo, int wtid) {
+                                                         uint8_t* lo, bool want_lo, int wtid, float4* v) {
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int ohw = p.cv_oh * p.cv_ow;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        const int o = row0 + r, m0 = k0 + c * 4;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (o < p.M && m0 < p.K) {
-            const int img = m0 / ohw, sp = m0 - img * ohw;
-            const float* src = p.A + ((long long)img * p.M + o) * ohw + sp;
-            if (p.a_vec_ok) {  // ohw % 4 == 0: the four positions lie in one image, 16-byte aligned
-                const float4 t = __ldg(reinterpret_cast<const float4*>(src));
-                x4[0] = t.x, x4[1] = t.y, x4[2] = t.z, x4[3] = t.w;
-            } else {
-                int ii = img, ss = sp;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (m0 + e < p.K) x4[e] = __ldg(p.A + ((long long)ii * p.M + o) * ohw + ss);
-                    if (++ss == ohw) ss = 0, ++ii;
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            const int o = row0 + r, m0 = k0 + c * 4;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (o < p.M && m0 < p.K) {
+                const int img = m0 / ohw, sp = m0 - img * ohw;
+                const float* src = p.A + ((long long)img * p.M + o) * ohw + sp;
+                if (p.a_vec_ok) {  // ohw % 4 == 0: the four positions lie in one image, 16-byte aligned
+                    const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+                    x4[0] = t.x, x4[1] = t.y, x4[2] = t.z, x4[3] = t.w;
+                } else {
+                    int ii = img, ss = sp;
+    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (m0 + e < p.K) x4[e] = __ldg(p.A + ((long long)ii * p.M + o) * ohw + ss);
+                        if (++ss == ohw) ss = 0, ++ii;
+                    }
                 }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        if (row0 + r < p.M) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            if (row0 + r < p.M) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+        }
     }
 }
 
 // B tile of the weight gradient: row = column kc = (c, kh, kw) of the column matrix, k = m,
 // gathered from x (N, C, H, W) exactly as nn::im2col would have filled cols[m][kc]
 // (src/conv.cpp:61-150).  Rows past C*kH*kW are left as they are (columns that are never stored).
-template <int ROWS>
+template <int ROWS, bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
-                                                        uint8_t* lo, bool want_lo, int wtid) {
+                                                        uint8_t* lo, bool want_lo, int wtid, float4* v) {
     constexpr int kPer = ROWS * 8 / kWorkerThreads;
     const int ohw = p.cv_oh * p.cv_ow, khw = p.cv_kh * p.cv_kw;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        const int kc = row0 + r, m0 = k0 + c * 4;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (kc == p.cv_ones_col) {
-            // the bias gradient rides along as one more column of the column matrix: dOut^T x 1
-#pragma unroll
-            for (int e = 0; e < 4; ++e) x4[e] = (m0 + e < p.K) ? 1.0f : 0.0f;
-        } else if (kc < p.N && m0 < p.K) {
-            const int ci = kc / khw, rem = kc - ci * khw;
-            const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-            int img = m0 / ohw;
-            const int pix = m0 - img * ohw;
-            int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (m0 + e < p.K) {
-                    const int ih = oh * p.cv_stride - p.cv_pad + kh, iw = ow * p.cv_stride - p.cv_pad + kw;
-                    if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w)
-                        x4[e] = __ldg(p.B + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
-                }
-                if (++ow == p.cv_ow) {
-                    ow = 0;
-                    if (++oh == p.cv_oh) oh = 0, ++img;
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            const int kc = row0 + r, m0 = k0 + c * 4;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (kc == p.cv_ones_col) {
+                // the bias gradient rides along as one more column of the column matrix: dOut^T x 1
+    #pragma unroll
+                for (int e = 0; e < 4; ++e) x4[e] = (m0 + e < p.K) ? 1.0f : 0.0f;
+            } else if (kc < p.N && m0 < p.K) {
+                const int ci = kc / khw, rem = kc - ci * khw;
+                const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                int img = m0 / ohw;
+                const int pix = m0 - img * ohw;
+                int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
+    #pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (m0 + e < p.K) {
+                        const int ih = oh * p.cv_stride - p.cv_pad + kh, iw = ow * p.cv_stride - p.cv_pad + kw;
+                        if (ih >= 0 && ih < p.cv_h && iw >= 0 && iw < p.cv_w)
+                            x4[e] = __ldg(p.B + (((long long)img * p.cv_c + ci) * p.cv_h + ih) * p.cv_w + iw);
+                    }
+                    if (++ow == p.cv_ow) {
+                        ow = 0;
+                        if (++oh == p.cv_oh) oh = 0, ++img;
+                    }
                 }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+        }
     }
 }
 
@@ -483,77 +505,84 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
 // taken over the terms whose divisions are exact and land inside dy.
 //
 // A tile: row = input pixel m' = (n, ih, iw), k = (o, kh, kw), gathered from dy.
+template <bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
-                                                           uint8_t* lo, bool want_lo, int wtid) {
+                                                           uint8_t* lo, bool want_lo, int wtid, float4* v) {
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int hw = p.cv_h * p.cv_w, khw = p.cv_kh * p.cv_kw;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit % kBM, c = unit / kBM;
-        const int gr = row0 + r;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (gr < p.M) {
-            const int img = gr / hw, pix = gr - img * hw;
-            const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int gk = k0 + c * 4 + e;
-                if (gk < p.K) {
-                    const int o = gk / khw, rem = gk - o * khw;
-                    const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
-                    int ty = ih + p.cv_pad - kh, tx = iw + p.cv_pad - kw;
-                    bool hit = ty >= 0 && tx >= 0;
-                    if (p.cv_stride != 1 && hit) {
-                        const int oy = ty / p.cv_stride, ox = tx / p.cv_stride;
-                        hit = oy * p.cv_stride == ty && ox * p.cv_stride == tx;
-                        ty = oy, tx = ox;
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit % kBM, c = unit / kBM;
+            const int gr = row0 + r;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gr < p.M) {
+                const int img = gr / hw, pix = gr - img * hw;
+                const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
+    #pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int gk = k0 + c * 4 + e;
+                    if (gk < p.K) {
+                        const int o = gk / khw, rem = gk - o * khw;
+                        const int kh = rem / p.cv_kw, kw = rem - kh * p.cv_kw;
+                        int ty = ih + p.cv_pad - kh, tx = iw + p.cv_pad - kw;
+                        bool hit = ty >= 0 && tx >= 0;
+                        if (p.cv_stride != 1 && hit) {
+                            const int oy = ty / p.cv_stride, ox = tx / p.cv_stride;
+                            hit = oy * p.cv_stride == ty && ox * p.cv_stride == tx;
+                            ty = oy, tx = ox;
+                        }
+                        if (hit && ty < p.cv_oh && tx < p.cv_ow)
+                            x4[e] = __ldg(p.A + (((long long)img * p.cv_oc + o) * p.cv_oh + ty) * p.cv_ow + tx);
                     }
-                    if (hit && ty < p.cv_oh && tx < p.cv_ow)
-                        x4[e] = __ldg(p.A + (((long long)img * p.cv_oc + o) * p.cv_oh + ty) * p.cv_ow + tx);
                 }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        store_unit_split(hi, lo, want_lo, unit % kBM, unit / kBM, v[u]);
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            store_unit_split(hi, lo, want_lo, unit % kBM, unit / kBM, v[u]);
+        }
     }
 }
 
 // B tile of the input gradient: row = input channel c, k = (o, kh, kw), read from the weight
 // (outC, C, kH, kW) as it is stored.  Rows past C are left as they are.
-template <int ROWS>
+template <int ROWS, bool kLoad, bool kStore>
 __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, int row0, int k0, uint8_t* hi,
-                                                          uint8_t* lo, bool want_lo, int wtid) {
+                                                          uint8_t* lo, bool want_lo, int wtid, float4* v) {
     constexpr int kPer = ROWS * 8 / kWorkerThreads;
     const int khw = p.cv_kh * p.cv_kw;
-    float4 v[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        const int ci = row0 + r;
-        float x4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (ci < p.N) {
-            int gk = k0 + c * 4;
-            int o = gk / khw, q = gk - o * khw;
-#pragma unroll
-            for (int e = 0; e < 4; ++e, ++gk) {
-                if (gk < p.K) x4[e] = __ldg(p.B + ((long long)o * p.cv_c + ci) * khw + q);
-                if (++q == khw) q = 0, ++o;
+    if constexpr (kLoad) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            const int ci = row0 + r;
+            float x4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (ci < p.N) {
+                int gk = k0 + c * 4;
+                int o = gk / khw, q = gk - o * khw;
+    #pragma unroll
+                for (int e = 0; e < 4; ++e, ++gk) {
+                    if (gk < p.K) x4[e] = __ldg(p.B + ((long long)o * p.cv_c + ci) * khw + q);
+                    if (++q == khw) q = 0, ++o;
+                }
             }
+            v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
         }
-        v[u] = make_float4(x4[0], x4[1], x4[2], x4[3]);
     }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int unit = wtid + u * kWorkerThreads;
-        const int r = unit >> 3, c = unit & 7;
-        if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+    if constexpr (kStore) {
+    #pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int unit = wtid + u * kWorkerThreads;
+            const int r = unit >> 3, c = unit & 7;
+            if (row0 + r < p.N) store_unit_split(hi, lo, want_lo, r, c, v[u]);
+        }
     }
 }
 
@@ -572,6 +601,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
     static_assert(!kPair || kTma, "pair mode loads with TMA");
     static_assert(kConv == 0 || !kTma, "the convolution gathers its operands in registers");
+    // the workers of the widest tiles (and of the register-staged loader, which also holds the next
+    // k-block in registers) take the control warpgroup's spare registers
+    constexpr bool kMoveRegs = BN == 256 || (!kTma && BN == 128);
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -635,7 +667,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     // The 128 x 256 tile keeps 128 accumulators per worker thread in registers: hand the
     // control warpgroup's registers to the two worker warpgroups.
     if (warp < kFirstWorkerWarp) {
-      if constexpr (BN == 256) reg_dealloc<40>();
+      if constexpr (kMoveRegs) reg_dealloc<40>();
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (kTma && lane == 0) {
@@ -786,7 +818,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
       }
     } else {
         // ------------------------------------------------------------------ workers
-        if constexpr (BN == 256) reg_alloc<232>();
+        if constexpr (kMoveRegs) reg_alloc<232>();
         const int wid = warp - kFirstWorkerWarp;
         const int wtid = threadIdx.x - kFirstWorkerWarp * 32;
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*quarter .. +31
@@ -876,12 +908,54 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             return true;
         };
 
+        // Register-staged loader: one k-block of both operands, as a load phase (global -> registers)
+        // and a store phase (split, registers -> shared memory), so that the loads of k-block i + 1
+        // are in flight while k-block i is multiplied and drained.
+        [[maybe_unused]] float4 va[kBM * 8 / kWorkerThreads];
+        [[maybe_unused]] float4 vb[BN * 8 / kWorkerThreads];
+        [[maybe_unused]] ConvRow crow{0, 0, 0};
+        [[maybe_unused]] auto ldg_phase = [&](auto load_c, auto store_c, const Work& wk, int kb, uint8_t* stage) {
+            constexpr bool L = decltype(load_c)::value, S = decltype(store_c)::value;
+            const int k0 = kb * BK;
+            uint8_t* a_hi = stage;
+            uint8_t* a_lo = stage + Cfg::kHalf;
+            uint8_t* b_hi = stage + Cfg::kABytes;
+            uint8_t* b_lo = stage + Cfg::kHalf + Cfg::kABytes;
+            if constexpr (kConv == 1) {
+                if (koff != nullptr) {
+                    conv_table_gather_split_store<L, S>(p.A, koff, kdelta, crow, p.cv_h, p.cv_w, k0, p.K, a_hi, a_lo,
+                                                        prec3, wtid, va);
+                } else {
+                    conv_gather_split_store<L, S>(p, wk.mt * kBM, k0, a_hi, a_lo, prec3, wtid, va);
+                }
+            } else if constexpr (kConv == 2) {
+                conv_dy_rows_split_store<L, S>(p, wk.mt * kBM, k0, a_hi, a_lo, prec3, wtid, va);
+            } else if constexpr (kConv == 3) {
+                if (koff != nullptr) {
+                    conv_table_gather_split_store<L, S>(p.A, koff, kdelta, crow, p.cv_oh, p.cv_ow, k0, p.K, a_hi,
+                                                        a_lo, prec3, wtid, va);
+                } else {
+                    conv_dx_gather_split_store<L, S>(p, wk.mt * kBM, k0, a_hi, a_lo, prec3, wtid, va);
+                }
+            } else {
+                ldg_split_store<kBM, L, S>(p.A + (long long)wk.b * p.strideA, p.lda, !p.transA, p.a_vec_ok != 0,
+                                           wk.mt * kBM, p.M, k0, p.K, a_hi, a_lo, prec3, wtid, va);
+            }
+            if constexpr (kConv == 2) {
+                conv_cols_T_split_store<BN, L, S>(p, wk.nt * BN, k0, b_hi, b_lo, prec3, wtid, vb);
+            } else if constexpr (kConv == 3) {
+                conv_weight_T_split_store<BN, L, S>(p, wk.nt * BN, k0, b_hi, b_lo, prec3, wtid, vb);
+            } else {
+                ldg_split_store<BN, L, S>(p.B + (long long)wk.b * p.strideB, p.ldb, p.transB != 0, p.b_vec_ok != 0,
+                                          wk.nt * BN, p.N, k0, p.K, b_hi, b_lo, prec3, wtid, vb);
+            }
+        };
+
         for (int w = first_work; w < p.total_work && ok; w += work_stride) {
             const Work wk = decode_work(p, w);
             const int nkb = wk.kb1 - wk.kb0;
 #pragma unroll
             for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
-            ConvRow crow{0, 0, 0};
             if constexpr (kConv == 1 || kConv == 3) {
                 if (koff != nullptr) {
                     const int gr = wk.mt * kBM + wtid % kBM;
@@ -908,6 +982,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 }
             }
 
+            if constexpr (!kTma) {
+                if (nkb > 0) ldg_phase(std::true_type{}, std::false_type{}, wk, wk.kb0, nullptr);
+            }
             for (int i = 0; i < nkb && ok; ++i, ++it) {
                 const uint32_t s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
@@ -955,46 +1032,17 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         break;
                     }
                     B200_T0();
-                    const int k0 = (wk.kb0 + i) * BK;
-                    const float* a_base = p.A + (long long)wk.b * p.strideA;
-                    const float* b_base = p.B + (long long)wk.b * p.strideB;
-                    if constexpr (kConv == 1) {
-                        if (koff != nullptr) {
-                            conv_table_gather_split_store(p.A, koff, kdelta, crow, p.cv_h, p.cv_w, k0, p.K, stage,
-                                                          stage + Cfg::kHalf, prec3, wtid);
-                        } else {
-                            conv_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
-                        }
-                    } else if constexpr (kConv == 2) {
-                        conv_dy_rows_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
-                    } else if constexpr (kConv == 3) {
-                        if (koff != nullptr) {
-                            conv_table_gather_split_store(p.A, koff, kdelta, crow, p.cv_oh, p.cv_ow, k0, p.K, stage,
-                                                          stage + Cfg::kHalf, prec3, wtid);
-                        } else {
-                            conv_dx_gather_split_store(p, wk.mt * kBM, k0, stage, stage + Cfg::kHalf, prec3, wtid);
-                        }
-                    } else {
-                        ldg_split_store<kBM>(a_base, p.lda, !p.transA, p.a_vec_ok != 0, wk.mt * kBM,
-                                             p.M, k0, p.K, stage, stage + Cfg::kHalf, prec3, wtid);
-                    }
-                    if constexpr (kConv == 2) {
-                        conv_cols_T_split_store<BN>(p, wk.nt * BN, k0, stage + Cfg::kABytes,
-                                                    stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
-                    } else if constexpr (kConv == 3) {
-                        conv_weight_T_split_store<BN>(p, wk.nt * BN, k0, stage + Cfg::kABytes,
-                                                      stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
-                    } else {
-                        ldg_split_store<BN>(b_base, p.ldb, p.transB != 0, p.b_vec_ok != 0, wk.nt * BN,
-                                            p.N, k0, p.K, stage + Cfg::kABytes,
-                                            stage + Cfg::kHalf + Cfg::kABytes, prec3, wtid);
-                    }
+                    ldg_phase(std::false_type{}, std::true_type{}, wk, wk.kb0 + i, stage);
                     B200_T1(6);
                 }
                 // generic-proxy writes -> visible to the tensor core's async-proxy reads
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) arrive_at_leader(smem_u32(&split_bar[s]));
+                if constexpr (!kTma) {
+                    // the next k-block's global loads fly while the accumulator is drained
+                    if (i + 1 < nkb) ldg_phase(std::true_type{}, std::false_type{}, wk, wk.kb0 + i + 1, nullptr);
+                }
 
                 // Drain the chain that ended one k-block ago (its MMAs have had a whole
                 // k-block of time to finish, so this rarely waits).
@@ -1160,23 +1208,35 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     }
 }
 
-// C = alpha * sum_s partial[s] + beta * C, splits added in ascending order so the result does
-// not depend on scheduling.  One thread per output element.
+// Adds the split-K partials (split x batch x M x N, one matrix after the other) into C and applies
+// the epilogue.  `lanes` (a power of two up to 32) threads share one element: lane j adds parts
+// j, j + lanes, ... in ascending order, then a fixed shuffle tree adds the lanes — the same order
+// on every run.  Few elements with many parts (a weight gradient contracted over a whole batch)
+// would otherwise leave one thread walking hundreds of parts a whole matrix apart.
 __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict__ partial,
                                      float* __restrict__ C, int split, long long batch, long long M,
                                      long long N, long long ldc, long long strideC, float alpha,
-                                     float beta) {
+                                     float beta, int lanes) {
     const long long total = batch * M * N;
-    const long long step = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & (lanes - 1);
+    const int per_warp = 32 / lanes;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long i0 = warp * per_warp; i0 < total; i0 += warps * per_warp) {
+        const long long i = i0 + lane / lanes;
         float s = 0.f;
-        for (int k = 0; k < split; ++k) s += partial[(long long)k * total + i];
-        const long long b = i / (M * N);
-        const long long r = (i - b * M * N) / N;
-        const long long c = i - b * M * N - r * N;
-        float* out = C + b * strideC + r * ldc + c;
-        *out = finish_output(p, alpha * s, beta != 0.f ? *out : 0.f, static_cast<int>(r),
-                             static_cast<int>(c));
+        if (i < total)
+            for (int k = sub; k < split; k += lanes) s += partial[(long long)k * total + i];
+        for (int off = lanes >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (i < total && sub == 0) {
+            const long long b = i / (M * N);
+            const long long r = (i - b * M * N) / N;
+            const long long c = i - b * M * N - r * N;
+            float* out = C + b * strideC + r * ldc + c;
+            *out = finish_output(p, alpha * s, beta != 0.f ? *out : 0.f, static_cast<int>(r),
+                                 static_cast<int>(c));
+        }
     }
 }
 

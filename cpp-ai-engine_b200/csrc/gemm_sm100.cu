@@ -610,11 +610,14 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     }
     if (pl.split_k > 1) {
         const int64_t elems = batch * M * N;
-        int blocks = static_cast<int>((elems + 255) / 256);
+        const int64_t max_threads = static_cast<int64_t>(st.sm_count) * 8 * 256;
+        int lanes = 1;  // threads per element: as many as the parts and the GPU allow
+        while (lanes < 32 && lanes * 2 <= pl.split_k && elems * lanes * 2 <= max_threads) lanes *= 2;
+        int blocks = static_cast<int>((elems * lanes + 255) / 256);
         if (blocks > st.sm_count * 8) blocks = st.sm_count * 8;
         splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p, static_cast<const float*>(workspace), C,
                                                          pl.split_k, batch, M, N, ldc, strideC,
-                                                         alpha, beta);
+                                                         alpha, beta, lanes);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         rc = static_cast<int>(cudaGetLastError());
     }
