@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <fstream>
 #include <numeric>
@@ -607,6 +608,283 @@ void Tensor::backward(const Tensor& grad_output) {
         if (node->backward_fn && node->grad) node->backward_fn(Tensor(node->grad));
     }
 }
+
+// ------------------------------------------------------------------------------- nn
+namespace nn {
+
+namespace {
+
+int current_precision() {
+    return g_kernel == cuda::MatmulKernel::TensorCore ? B200_PRECISION_TF32 : B200_PRECISION_3XTF32;
+}
+
+const std::shared_ptr<TensorImpl>& impl_of(const Tensor& t) { return TensorImpl::of(t); }
+
+// Row-major values of a tensor on the device (a transposed view is first copied into logical order).
+Tensor contiguous(const Tensor& t) {
+    if (!t.is_transposed_view()) return t;
+    if (g_grad_enabled && t.requires_grad()) {
+        throw std::invalid_argument("A layer operand that requires a gradient must not be a transposed view.");
+    }
+    return Tensor(t.shape(), t.to_vector());
+}
+
+// The gradient buffer of `x`, created on first use; returns the beta to accumulate with.
+float* grad_buffer(TensorImpl& x, float* beta) {
+    *beta = x.grad ? 1.0f : 0.0f;
+    if (!x.grad) {
+        auto p = make_impl(x.shape, Storage(product(x.shape), 0.0f), false);
+        x.grad = p;
+    }
+    return *beta == 0.0f ? x.grad->storage.device_write() : x.grad->storage.device_mut();
+}
+
+}  // namespace
+
+void Window2d::validate(size_t in_h, size_t in_w) const {
+    if (kernel_h == 0 || kernel_w == 0 || stride == 0) {
+        throw std::invalid_argument("Window2d requires a kernel and a stride greater than zero.");
+    }
+    if (in_h + 2 * padding < kernel_h || in_w + 2 * padding < kernel_w) {
+        throw std::invalid_argument("The window does not fit the padded input.");
+    }
+}
+
+Tensor linear(const Tensor& input_, const Tensor& weight_, const Tensor* bias, bool relu) {
+    if (input_.ndim() < 2) {
+        throw std::invalid_argument("Linear expects at least 2 dimensions (..., in_features), received " +
+                                    input_.shape_str() + ".");
+    }
+    if (weight_.ndim() != 2) throw std::invalid_argument("Linear expects a 2-D weight (in, out).");
+    const size_t in_f = weight_.shape()[0], out_f = weight_.shape()[1];
+    if (input_.shape().back() != in_f) {
+        throw std::invalid_argument("Linear with in_features=" + std::to_string(in_f) + " received an input " +
+                                    input_.shape_str() + ".");
+    }
+    if (bias != nullptr && bias->size() != out_f) {
+        throw std::invalid_argument("Linear expects one bias value per output feature.");
+    }
+    const Tensor input = contiguous(input_), weight = contiguous(weight_);
+    const size_t rows = input.size() / in_f;
+    std::vector<size_t> out_shape = input.shape();
+    out_shape.back() = out_f;
+    const bool tracked = g_grad_enabled && !relu &&
+                         (input.requires_grad() || weight.requires_grad() || (bias && bias->requires_grad()));
+    Tensor out(out_shape, 0.0f, tracked);
+    if (rows == 0) return out;
+
+    b200_epilogue ep{};
+    ep.bias = bias ? impl_of(*bias)->storage.device() : nullptr;
+    ep.relu = relu ? 1 : 0;
+    const int64_t m = static_cast<int64_t>(rows), k = static_cast<int64_t>(in_f), n = static_cast<int64_t>(out_f);
+    const size_t ws_bytes = b200_gemm_f32_workspace(1, m, n, k);
+    void* ws = ws_bytes ? g_scratch.get(ws_bytes) : nullptr;
+    float* dst = impl_of(out)->storage.device_write();
+    check_b200(b200_gemm_f32_fused(impl_of(input)->storage.device(), impl_of(weight)->storage.device(), dst, 1, m,
+                                   n, k, 0, 0, k, n, n, 0, 0, m * n, 1.0f, 0.0f, current_precision(), &ep, ws,
+                                   ws_bytes, nullptr),
+               "linear");
+    if (!tracked) return out;
+
+    auto xi = impl_of(input), wi = impl_of(weight);
+    std::shared_ptr<TensorImpl> bi = bias ? impl_of(*bias) : nullptr;
+    impl_of(out)->parents = {xi, wi};
+    if (bi) impl_of(out)->parents.push_back(bi);
+    impl_of(out)->backward_fn = [xi, wi, bi, rows, in_f, out_f](const Tensor& grad_out) {
+        const Tensor g = contiguous(grad_out);
+        const float* pg = impl_of(g)->storage.device();
+        float beta = 0.0f;
+        if (xi->requires_grad) {  // dX (rows x in) = g (rows x out) x W^T
+            float* o = grad_buffer(*xi, &beta);
+            raw_gemm(pg, wi->storage.device(), o, 1, rows, out_f, in_f, false, true, 0, 0, beta);
+        }
+        if (wi->requires_grad) {  // dW (in x out) = X^T x g
+            float* o = grad_buffer(*wi, &beta);
+            raw_gemm(xi->storage.device(), pg, o, 1, in_f, rows, out_f, true, false, 0, 0, beta);
+        }
+        if (bi && bi->requires_grad) {  // db (1 x out) = ones (1 x rows) x g
+            const Storage ones(rows, 1.0f);
+            float* o = grad_buffer(*bi, &beta);
+            raw_gemm(ones.device(), pg, o, 1, 1, rows, out_f, false, false, 0, 0, beta);
+        }
+    };
+    return out;
+}
+
+Tensor conv2d(const Tensor& input_, const Tensor& weight_, const Tensor* bias, const Window2d& window) {
+    if (input_.ndim() != 4) {
+        throw std::invalid_argument("Conv2d expects a 4D volume (N, C, H, W), received " + input_.shape_str() + ".");
+    }
+    if (weight_.ndim() != 4 || weight_.shape()[2] != window.kernel_h || weight_.shape()[3] != window.kernel_w) {
+        throw std::invalid_argument("Conv2d expects a weight (outC, C, kH, kW) matching the window.");
+    }
+    if (input_.shape()[1] != weight_.shape()[1]) {
+        throw std::invalid_argument("Conv2d with in_channels=" + std::to_string(weight_.shape()[1]) +
+                                    " received an input " + input_.shape_str() + ".");
+    }
+    const size_t N = input_.shape()[0], C = input_.shape()[1], H = input_.shape()[2], W = input_.shape()[3];
+    const size_t out_c = weight_.shape()[0];
+    window.validate(H, W);
+    if (bias != nullptr && bias->size() != out_c) {
+        throw std::invalid_argument("Conv2d expects one bias value per output channel.");
+    }
+    const Tensor input = contiguous(input_), weight = contiguous(weight_);
+    const size_t oH = window.out_h(H), oW = window.out_w(W);
+    const bool tracked = g_grad_enabled &&
+                         (input.requires_grad() || weight.requires_grad() || (bias && bias->requires_grad()));
+    Tensor out({N, out_c, oH, oW}, 0.0f, tracked);
+    if (out.size() == 0) return out;
+    const auto i64 = [](size_t v) { return static_cast<int64_t>(v); };
+    check_b200(b200_conv2d_forward_f32(impl_of(input)->storage.device(), impl_of(weight)->storage.device(),
+                                       bias ? impl_of(*bias)->storage.device() : nullptr,
+                                       impl_of(out)->storage.device_write(), i64(N), i64(C), i64(H), i64(W),
+                                       i64(out_c), i64(window.kernel_h), i64(window.kernel_w), i64(window.stride),
+                                       i64(window.padding), 0, current_precision(), nullptr),
+               "conv2d forward");
+    if (!tracked) return out;
+
+    auto xi = impl_of(input), wi = impl_of(weight);
+    std::shared_ptr<TensorImpl> bi = bias ? impl_of(*bias) : nullptr;
+    impl_of(out)->parents = {xi, wi};
+    if (bi) impl_of(out)->parents.push_back(bi);
+    const Window2d win = window;
+    impl_of(out)->backward_fn = [xi, wi, bi, win, N, C, H, W, out_c](const Tensor& grad_out) {
+        const Tensor g = contiguous(grad_out);
+        const auto i64 = [](size_t v) { return static_cast<int64_t>(v); };
+        // A gradient that already exists is accumulated into (Tensor::add_grad), a new one is
+        // written: at most one call for each of the two cases.
+        float* fresh[3] = {nullptr, nullptr, nullptr};
+        float* accum[3] = {nullptr, nullptr, nullptr};
+        TensorImpl* targets[3] = {xi->requires_grad ? xi.get() : nullptr, wi->requires_grad ? wi.get() : nullptr,
+                                  bi && bi->requires_grad ? bi.get() : nullptr};
+        for (int which = 0; which < 3; ++which) {
+            if (targets[which] == nullptr) continue;
+            float beta = 0.0f;
+            float* buf = grad_buffer(*targets[which], &beta);
+            (beta == 0.0f ? fresh : accum)[which] = buf;
+        }
+        auto run = [&](float* const o[3], float beta) {
+            if (o[0] == nullptr && o[1] == nullptr && o[2] == nullptr) return;
+            const size_t ws_bytes = o[1] ? b200_conv2d_backward_workspace(
+                                               i64(N), i64(C), i64(H), i64(W), i64(out_c), i64(win.kernel_h),
+                                               i64(win.kernel_w), i64(win.stride), i64(win.padding))
+                                         : 0;
+            void* ws = ws_bytes ? g_scratch.get(ws_bytes) : nullptr;
+            check_b200(b200_conv2d_backward_f32(xi->storage.device(), wi->storage.device(),
+                                                impl_of(g)->storage.device(), o[0], o[1], o[2], i64(N), i64(C),
+                                                i64(H), i64(W), i64(out_c), i64(win.kernel_h), i64(win.kernel_w),
+                                                i64(win.stride), i64(win.padding), beta, current_precision(), ws,
+                                                ws_bytes, nullptr),
+                       "conv2d backward");
+        };
+        run(fresh, 0.0f);
+        run(accum, 1.0f);
+    };
+    return out;
+}
+
+namespace {
+
+void attention_checks(const Tensor& q, const Tensor& k, const Tensor& v) {
+    if (q.requires_grad() || k.requires_grad() || v.requires_grad()) {
+        if (g_grad_enabled) {
+            throw std::invalid_argument(
+                "The fused attention kernel is forward-only: run it on detached tensors, or train through "
+                "the separate products.");
+        }
+    }
+}
+
+const float* mask_pointer(const Tensor* mask, size_t s_q, size_t s_k, Tensor* keep) {
+    if (mask == nullptr) return nullptr;
+    if (mask->ndim() != 2 || mask->shape()[0] != s_q || mask->shape()[1] != s_k) {
+        throw std::invalid_argument("The attention mask must be (S_q, S_k), received " + mask->shape_str() + ".");
+    }
+    *keep = contiguous(*mask);
+    return impl_of(*keep)->storage.device();
+}
+
+}  // namespace
+
+Tensor scaled_dot_product_attention(const Tensor& query_, const Tensor& key_, const Tensor& value_,
+                                    const Tensor* mask, Tensor* attention_weights) {
+    if (query_.ndim() < 2 || key_.ndim() < 2 || value_.ndim() < 2) {
+        throw std::invalid_argument("Attention needs at least 2 dimensions (seq, d_k).");
+    }
+    const size_t d_k = query_.shape().back();
+    if (key_.shape().back() != d_k) {
+        throw std::invalid_argument("Query and key must share d_k: " + query_.shape_str() + " and " +
+                                    key_.shape_str() + ".");
+    }
+    attention_checks(query_, key_, value_);
+    const Tensor q = contiguous(query_), k = contiguous(key_), v = contiguous(value_);
+    const std::vector<size_t> lead(q.shape().begin(), q.shape().end() - 2);
+    const size_t s_q = q.shape()[q.ndim() - 2], s_k = k.shape()[k.ndim() - 2], d_v = v.shape().back();
+    if (std::vector<size_t>(k.shape().begin(), k.shape().end() - 2) != lead ||
+        std::vector<size_t>(v.shape().begin(), v.shape().end() - 2) != lead || v.shape()[v.ndim() - 2] != s_k) {
+        throw std::invalid_argument("Batched MatMul needs identical batch axes: " + q.shape_str() + ", " +
+                                    k.shape_str() + " and " + v.shape_str() + ".");
+    }
+    Tensor mask_keep;
+    const float* pm = mask_pointer(mask, s_q, s_k, &mask_keep);
+    std::vector<size_t> out_shape = lead, w_shape = lead;
+    out_shape.insert(out_shape.end(), {s_q, d_v});
+    w_shape.insert(w_shape.end(), {s_q, s_k});
+    Tensor out(out_shape, 0.0f, false);
+    Tensor weights = attention_weights ? Tensor(w_shape, 0.0f, false) : Tensor();
+    const size_t batch = product(lead);
+    if (batch == 0) return out;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(d_k));
+    const auto i64 = [](size_t x) { return static_cast<int64_t>(x); };
+    check_b200(b200_attention_f32(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
+                                  impl_of(v)->storage.device(), pm, impl_of(out)->storage.device_write(),
+                                  attention_weights ? impl_of(weights)->storage.device_write() : nullptr,
+                                  i64(batch), i64(s_q), i64(s_k), i64(d_k), i64(d_v), scale, current_precision(),
+                                  nullptr),
+               "scaled_dot_product_attention");
+    if (attention_weights) *attention_weights = weights;
+    return out;
+}
+
+Tensor multi_head_attention_core(const Tensor& query_, const Tensor& key_, const Tensor& value_,
+                                 size_t num_heads, const Tensor* mask) {
+    for (const Tensor* t : {&query_, &key_, &value_}) {
+        if (t->ndim() != 3) {
+            throw std::invalid_argument("MultiHeadAttention expects (batch, seq, d_model), received " +
+                                        t->shape_str() + ".");
+        }
+    }
+    const size_t batch = query_.shape()[0], s_q = query_.shape()[1], d_model = query_.shape()[2];
+    if (num_heads == 0 || d_model % num_heads != 0 || value_.shape()[2] % num_heads != 0) {
+        throw std::invalid_argument("d_model must be divisible by num_heads.");
+    }
+    if (key_.shape()[0] != batch || value_.shape()[0] != batch || key_.shape()[2] != d_model ||
+        key_.shape()[1] != value_.shape()[1]) {
+        throw std::invalid_argument("query, key and value need the same batch, key/value the same length and "
+                                    "query/key the same width.");
+    }
+    attention_checks(query_, key_, value_);
+    const Tensor q = contiguous(query_), k = contiguous(key_), v = contiguous(value_);
+    const size_t s_k = k.shape()[1], d_k = d_model / num_heads, dv_model = v.shape()[2], d_v = dv_model / num_heads;
+    Tensor mask_keep;
+    const float* pm = mask_pointer(mask, s_q, s_k, &mask_keep);
+    Tensor out({batch, s_q, dv_model}, 0.0f, false);
+    if (batch == 0) return out;
+    const auto i64 = [](size_t x) { return static_cast<int64_t>(x); };
+    const int64_t qs[3] = {i64(s_q * d_model), i64(d_k), i64(d_model)};
+    const int64_t ks[3] = {i64(s_k * d_model), i64(d_k), i64(d_model)};
+    const int64_t vs[3] = {i64(s_k * dv_model), i64(d_v), i64(dv_model)};
+    const int64_t os[3] = {i64(s_q * dv_model), i64(d_v), i64(dv_model)};
+    const float scale = 1.0f / std::sqrt(static_cast<float>(d_k));
+    check_b200(b200_attention_f32_strided(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
+                                          impl_of(v)->storage.device(), pm, impl_of(out)->storage.device_write(),
+                                          nullptr, i64(batch), i64(num_heads), i64(s_q), i64(s_k), i64(d_k),
+                                          i64(d_v), qs, ks, vs, os, scale, current_precision(), nullptr),
+               "multi_head_attention_core");
+    return out;
+}
+
+}  // namespace nn
 
 // ------------------------------------------------------------------------------- load_tensors
 std::vector<std::pair<std::string, Tensor>> load_tensors(const std::string& path) {

@@ -8,6 +8,11 @@
 //   engine::cuda::transfer_stats / kernels_launched       include/engine/cuda.hpp:79-81, 209-218
 //   engine::Tensor::matmul / transpose / reshape /        include/engine/tensor.hpp:157-198,
 //           backward / grad                               src/tensor_ops.cpp:475-588
+//   engine::nn::linear / conv2d / attention               the forward bodies of Linear (src/nn.cpp:101-130),
+//                                                         Conv2d (src/conv.cpp:280-338) and
+//                                                         scaled_dot_product_attention / MultiHeadAttention
+//                                                         (src/transformer.cpp:279-304, 332-357), each as
+//                                                         ONE kernel
 //
 // What differs, on purpose: there is no CPU loop (ops::matmul never returns false — it throws
 // when the device cannot run the product), transpose() is a zero-copy view that the product
@@ -163,6 +168,49 @@ private:
     std::shared_ptr<TensorImpl> impl_;
     friend struct TensorImpl;
 };
+
+namespace nn {
+
+// include/engine/conv.hpp:12-26.
+struct Window2d {
+    size_t kernel_h;
+    size_t kernel_w;
+    size_t stride = 1;
+    size_t padding = 0;
+
+    Window2d(size_t k) : kernel_h(k), kernel_w(k) {}
+    Window2d(size_t kh, size_t kw, size_t s = 1, size_t p = 0)
+        : kernel_h(kh), kernel_w(kw), stride(s), padding(p) {}
+    size_t out_h(size_t in_h) const { return (in_h + 2 * padding - kernel_h) / stride + 1; }
+    size_t out_w(size_t in_w) const { return (in_w + 2 * padding - kernel_w) / stride + 1; }
+    void validate(size_t in_h, size_t in_w) const;  // throws std::invalid_argument
+};
+
+// Linear::forward: input (..., in) x weight (in, out) + bias (out), optionally followed by ReLU
+// (the feed-forward ff1(x).relu(), src/transformer.cpp:413) — product, broadcast add and
+// activation in one kernel.  Gradients flow to input, weight and bias when relu is false (the
+// bias gradient is the column sum of the incoming gradient, taken as a product with a row of
+// ones); with relu the result does not track gradients.
+Tensor linear(const Tensor& input, const Tensor& weight, const Tensor* bias = nullptr, bool relu = false);
+
+// Conv2d::forward on (N, C, H, W) with weight (outC, C, kH, kW) and optional bias (outC): one
+// implicit-GEMM kernel; its backward is one call that fills the three gradients without a
+// column matrix (b200_conv2d_backward_f32).
+Tensor conv2d(const Tensor& input, const Tensor& weight, const Tensor* bias, const Window2d& window);
+
+// scaled_dot_product_attention over the leading (batch, head) axes: softmax(Q K^T / sqrt(d_k) +
+// mask) V in one kernel; attention_weights, if given, receives the softmax output.  Forward
+// only: throws std::invalid_argument if an operand requires a gradient (train through the
+// separate products).  Limits: S_q, S_k <= 128 and d_k, d_v <= 64 (std::runtime_error beyond).
+Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, const Tensor& value,
+                                    const Tensor* mask = nullptr, Tensor* attention_weights = nullptr);
+
+// The middle of MultiHeadAttention::forward: the three projections (B, S, d_model) in, the merged
+// context (B, S, d_model) out; heads are split and merged by addressing, not by permute copies.
+Tensor multi_head_attention_core(const Tensor& query, const Tensor& key, const Tensor& value,
+                                 size_t num_heads, const Tensor* mask = nullptr);
+
+}  // namespace nn
 
 // Reads every tensor of a file in the reference's documented container format
 // (include/engine/serialize.hpp:12-31: "CPPAIENG", u32 version, u32 count, then per tensor

@@ -5,6 +5,8 @@
 //   numerical gradients                       tests/test_tensor.cpp:245-258, tests/test_support.hpp:78-121
 //   CPU/GPU parity shape list, "a kernel must have run", residency / transfer counts
 //                                             tests/test_cuda_parity.cpp:62-137, 192-247, 790-818
+//   layers: Conv2d with gradients, attention, MultiHeadAttention
+//                                             tests/test_reference.cpp:216-251, 296-349 (abs tol 1e-4)
 // The CPU side of the parity checks is the oracle library (test infrastructure).
 #include "engine_b200.hpp"
 
@@ -280,6 +282,135 @@ void test_reduced_precision_is_opt_in() {
     check(e1 > 10.0 * e3, "tf32 is more than 10x less precise");
 }
 
+
+double max_abs_diff(const std::vector<float>& got, const std::vector<float>& want) {
+    if (got.size() != want.size()) return 1e30;
+    double worst = 0.0;
+    for (size_t i = 0; i < got.size(); ++i) worst = std::max(worst, std::fabs(double(got[i]) - double(want[i])));
+    return worst;
+}
+
+// The layer bodies as single kernels, against the reference's PyTorch vectors
+// (tests/test_reference.cpp:216-251 Conv2d with gradients, :296-349 attention and
+// MultiHeadAttention; abs tol 1e-4 as there) and against the oracle product for Linear.
+void test_layers(const std::string& golden_dir) {
+    section("Layers as single kernels (golden vectors)");
+    std::map<std::string, Tensor> f;
+    for (auto& kv : engine::load_tensors(golden_dir + "/pytorch_layers.bin")) f.emplace(kv.first, kv.second);
+    namespace nn = engine::nn;
+
+    struct ConvCase {
+        std::string name;
+        size_t stride, pad;
+    };
+    for (const ConvCase& cc : {ConvCase{"conv2d_pad1", 1, 1}, ConvCase{"conv2d_stride2", 2, 0}}) {
+        Tensor x = f.at(cc.name + "/input").detach();
+        Tensor w = f.at(cc.name + "/weight").detach();
+        Tensor b = f.at(cc.name + "/bias").detach();
+        x.set_requires_grad(true);
+        w.set_requires_grad(true);
+        b.set_requires_grad(true);
+        const size_t before = engine::cuda::kernels_launched();
+        Tensor y = nn::conv2d(x, w, &b, nn::Window2d(3, 3, cc.stride, cc.pad));
+        check(engine::cuda::kernels_launched() == before + 1, cc.name + ": the forward is one kernel");
+        check(max_abs_diff(y.to_vector(), f.at(cc.name + "/output").to_vector()) <= 1e-4, cc.name + ": output");
+        y.backward(f.at(cc.name + "/grad_output"));
+        check(max_abs_diff(x.grad().to_vector(), f.at(cc.name + "/grad.input").to_vector()) <= 1e-4,
+              cc.name + ": gradient of the input");
+        check(max_abs_diff(w.grad().to_vector(), f.at(cc.name + "/grad.weight").to_vector()) <= 1e-4,
+              cc.name + ": gradient of the kernel");
+        check(max_abs_diff(b.grad().to_vector(), f.at(cc.name + "/grad.bias").to_vector()) <= 1e-4,
+              cc.name + ": gradient of the bias");
+        // a second backward accumulates (Tensor::add_grad)
+        const std::vector<float> once = w.grad().to_vector();
+        Tensor y2 = nn::conv2d(x, w, &b, nn::Window2d(3, 3, cc.stride, cc.pad));
+        y2.backward(f.at(cc.name + "/grad_output"));
+        std::vector<float> twice = w.grad().to_vector(), want2(once.size());
+        for (size_t i = 0; i < once.size(); ++i) want2[i] = 2.0f * once[i];
+        check(max_abs_diff(twice, want2) <= 1e-4, cc.name + ": a second backward adds to the stored gradient");
+    }
+    check_throws([&] { nn::conv2d(Tensor({2, 3, 8}), Tensor({4, 3, 3, 3}), nullptr, nn::Window2d(3)); },
+                 "conv2d of a 3-D input throws");
+    check_throws([&] { nn::conv2d(Tensor({2, 2, 8, 8}), Tensor({4, 3, 3, 3}), nullptr, nn::Window2d(3)); },
+                 "conv2d with mismatched channels throws");
+
+    for (const std::string name : {"attention", "attention_causal"}) {
+        const bool has_mask = f.count(name + "/mask") != 0;
+        Tensor mask = has_mask ? f.at(name + "/mask") : Tensor();
+        Tensor weights;
+        const size_t before = engine::cuda::kernels_launched();
+        Tensor out = nn::scaled_dot_product_attention(f.at(name + "/q"), f.at(name + "/k"), f.at(name + "/v"),
+                                                      has_mask ? &mask : nullptr, &weights);
+        check(engine::cuda::kernels_launched() == before + 1, name + ": one kernel");
+        check(max_abs_diff(out.to_vector(), f.at(name + "/output").to_vector()) <= 1e-4, name + ": output");
+        const std::vector<float> wv = weights.to_vector();
+        const size_t s_k = weights.shape().back();
+        double worst = 0.0;
+        for (size_t r = 0; r < wv.size() / s_k; ++r) {
+            double sum = 0.0;
+            for (size_t j = 0; j < s_k; ++j) sum += wv[r * s_k + j];
+            worst = std::max(worst, std::fabs(sum - 1.0));
+        }
+        check(worst <= 1e-5, name + ": attention weights sum to one per row");
+    }
+    {
+        Tensor q = f.at("attention/q").detach();
+        q.set_requires_grad(true);
+        check_throws([&] { nn::scaled_dot_product_attention(q, f.at("attention/k"), f.at("attention/v")); },
+                     "the fused attention refuses operands that require gradients");
+    }
+
+    // MultiHeadAttention(8, 2): four Linear layers around the strided attention core
+    {
+        Tensor x = f.at("multihead/input");
+        std::map<std::string, Tensor> proj;
+        for (const std::string tag : {"query", "key", "value"}) {
+            Tensor bias = f.at("multihead/w." + tag + ".bias");
+            proj.emplace(tag, nn::linear(x, f.at("multihead/w." + tag + ".weight"), &bias));
+        }
+        const size_t before = engine::cuda::kernels_launched();
+        Tensor merged = nn::multi_head_attention_core(proj.at("query"), proj.at("key"), proj.at("value"), 2);
+        check(engine::cuda::kernels_launched() == before + 1, "multihead: split, attention and merge are one kernel");
+        Tensor out_bias = f.at("multihead/w.out.bias");
+        Tensor out = nn::linear(merged, f.at("multihead/w.out.weight"), &out_bias);
+        check(max_abs_diff(out.to_vector(), f.at("multihead/output").to_vector()) <= 1e-4, "multihead: output");
+    }
+
+    section("Linear: fused bias / ReLU and gradients");
+    engine::manual_seed(21);
+    Tensor x = Tensor::randn({4, 33, 96}, 0.0f, 1.0f, true);
+    Tensor w = Tensor::rand({96, 121}, -0.17f, 0.17f, true);
+    Tensor b = Tensor::randn({121}, 0.0f, 1.0f, true);
+    {
+        const size_t before = engine::cuda::kernels_launched();
+        Tensor y = nn::linear(x, w, &b);
+        check(engine::cuda::kernels_launched() == before + 1, "linear: product and bias are one kernel");
+        std::vector<float> want = oracle_matmul(x.reshape({4 * 33, 96}), w), bv = b.to_vector();
+        for (size_t i = 0; i < want.size(); ++i) want[i] += bv[i % 121];
+        check(y.shape() == std::vector<size_t>({4, 33, 121}), "linear: the leading axes are restored");
+        check(scaled_error(y.to_vector(), want) <= tolerance(96), "linear: output against the CPU loop + bias");
+        std::vector<float> relu_want = want;
+        for (float& v : relu_want) v = std::max(v, 0.0f);
+        check(scaled_error(nn::linear(x, w, &b, true).to_vector(), relu_want) <= tolerance(96),
+              "linear: fused ReLU");
+        Tensor g = Tensor::randn({4, 33, 121});
+        y.backward(g);
+        // the same gradients through the plain product
+        Tensor x2 = x.detach().reshape({4 * 33, 96}), w2 = w.detach();
+        x2.set_requires_grad(true);
+        w2.set_requires_grad(true);
+        Tensor y2 = x2.matmul(w2);
+        y2.backward(g.reshape({4 * 33, 121}));
+        check(scaled_error(x.grad().to_vector(), x2.grad().to_vector()) <= 1e-5, "linear: gradient of the input");
+        check(scaled_error(w.grad().to_vector(), w2.grad().to_vector()) <= 1e-5, "linear: gradient of the weight");
+        std::vector<float> gv = g.to_vector(), db(121, 0.0f);
+        for (size_t r = 0; r < 4 * 33; ++r)
+            for (size_t c = 0; c < 121; ++c) db[c] += gv[r * 121 + c];
+        check(scaled_error(b.grad().to_vector(), db) <= tolerance(4 * 33), "linear: gradient of the bias");
+    }
+    check_throws([&] { nn::linear(Tensor({4, 95}), w); }, "linear with a wrong input width throws");
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -295,6 +426,7 @@ int main(int argc, char** argv) {
         test_parity_shapes();
         test_residency_and_seam();
         test_reduced_precision_is_opt_in();
+        test_layers(golden_dir);
         engine::cuda::check_device_status();
     } catch (const std::exception& e) {
         std::cout << "EXCEPTION: " << e.what() << "\n";

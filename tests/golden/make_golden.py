@@ -13,6 +13,8 @@ Outputs (small, committed):
                        seeded inputs (drawn from its own generator): inputs, output and the three gradients.
   pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward (tests/fixtures/attention*.bin).
   pytorch_multihead.npz  the same for a whole MultiHeadAttention forward (tests/fixtures/multihead_attention.bin).
+  pytorch_layers.bin   the Conv2d, attention and MultiHeadAttention vectors again, in the container format,
+                       for the C++ host tests.
   known_answers.json   the integer known-answer products of tests/test_tensor.cpp:47-65, 182-202.
   reference_runs.npz   outputs of the UNMODIFIED reference engine (oracle/_ref) on seeded
                        inputs: its random streams, and per configuration a SHA-256 of the full
@@ -174,6 +176,13 @@ def main() -> None:
     #     input, the four projections' weights (in, out) and biases, output
     fx = read_fixture(ref_dir / "tests" / "fixtures" / "multihead_attention.bin")
     np.savez(HERE / "pytorch_multihead.npz", **{k: v for k, v in fx.items() if not k.startswith("grad")})
+
+    # 1d'. the same layer vectors (Conv2d with gradients, attention, MultiHeadAttention) in the container
+    #      format, for the C++ host tests
+    layers = dict(conv)
+    layers.update(att)
+    layers.update({f"multihead/{k}": v for k, v in fx.items() if not k.startswith("grad")})
+    write_container(HERE / "pytorch_layers.bin", layers)
 
     # 1e. the reference engine's own Conv2d layer and autograd on seeded inputs
     cb = {}
