@@ -601,6 +601,27 @@ def run_engine_suite(args):
     time_layer("cfg2 attention, heads by strides (32,64,96)x3 -> (32,64,96)",
                lambda: pkg.multi_head_attention_core(qp, kp, vp, 4, mask), 1)
     time_layer("cfg2 attention, heads by permute copies + fused core", permuted, 5)
+    # The products of one char-LM Transformer block as five layer calls, eager and replayed from a CUDA
+    # graph (no host cost per launch): fused Q|K|V projection, attention on its column slices, output
+    # projection, FF1 + ReLU, FF2.
+    if not args.only or "block" in args.only:
+        xb = torch.randn((2048, 96), device=dev, generator=gen)
+        wb = {k: torch.randn(s_, device=dev, generator=gen) * 0.1
+              for k, s_ in (("qkv", (96, 288)), ("bqkv", (288,)), ("out", (96, 96)), ("bout", (96,)),
+                            ("ff1", (96, 384)), ("b1", (384,)), ("ff2", (384, 96)), ("b2", (96,)))}
+
+        def block():
+            qkv = pkg.linear(xb, wb["qkv"], wb["bqkv"]).view(32, 64, 288)
+            ctx = pkg.multi_head_attention_core(qkv[:, :, :96], qkv[:, :, 96:192], qkv[:, :, 192:], 4, mask)
+            o = pkg.linear(ctx.view(2048, 96), wb["out"], wb["bout"])
+            return pkg.linear(pkg.linear(o, wb["ff1"], wb["b1"], relu=True), wb["ff2"], wb["b2"])
+
+        time_layer("cfg2 block products, 5 layer calls (6 kernels), eager", block, 6)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            block()
+        time_layer("cfg2 block products, 5 layer calls (6 kernels), CUDA graph replay", graph.replay, 6,
+                   note="one replay = all six kernels; no host work per launch")
     # whole Conv2d layers (im2col + product + bias + permute in the reference) as one kernel, and
     # their gradients (product backward over the columns + col2im in the reference)
     import torch.nn.functional as F

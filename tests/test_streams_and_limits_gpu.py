@@ -98,3 +98,67 @@ def test_nan_and_zero_inputs_propagate_like_arithmetic(pkg, cuda):
     A[3, 5] = float("nan")
     out = pkg.matmul(A, B).cpu().numpy()
     assert np.isnan(out[3]).all() and not np.isnan(np.delete(out, 3, axis=0)).any()
+
+
+def _block_weights(orc, cuda):
+    g = orc.Rng(62)
+    d, ff = 96, 384
+    w = {
+        "qkv": g.rand((d, 3 * d), -0.125, 0.125), "bqkv": g.randn((3 * d,), 0.0, 0.1),
+        "out": g.rand((d, d), -0.17, 0.17), "bout": g.randn((d,), 0.0, 0.1),
+        "ff1": g.rand((d, ff), -0.11, 0.11), "b1": g.randn((ff,), 0.0, 0.1),
+        "ff2": g.rand((ff, d), -0.11, 0.11), "b2": g.randn((d,), 0.0, 0.1),
+    }
+    return {k: dev(v, cuda) for k, v in w.items()}
+
+
+def _block_products(pkg, x, w, mask):
+    """The products of one char-LM Transformer block (B = 32, S = 64, d = 96, 4 heads, FFN 384) as five
+    layer calls: fused Q|K|V projection, attention core on its column slices, output projection, FF1 + ReLU, FF2."""
+    qkv = pkg.linear(x, w["qkv"], w["bqkv"]).view(32, 64, 288)
+    ctx = pkg.multi_head_attention_core(qkv[:, :, :96], qkv[:, :, 96:192], qkv[:, :, 192:], 4, mask)
+    o = pkg.linear(ctx.view(2048, 96), w["out"], w["bout"])
+    h = pkg.linear(o, w["ff1"], w["b1"], relu=True)
+    return pkg.linear(h, w["ff2"], w["b2"])
+
+
+def test_block_chain_replays_from_a_cuda_graph(pkg, orc, cuda):
+    """The launches allocate nothing and synchronise nothing, so a chain of them can be captured once
+    and replayed: the replay on new inputs gives, bit for bit, what the eager calls give."""
+    import torch
+
+    w = _block_weights(orc, cuda)
+    mask = torch.triu(torch.full((64, 64), -1e9, device=cuda), 1)
+    g = orc.Rng(63)
+    x_static = dev(g.randn((2048, 96)), cuda)
+    _block_products(pkg, x_static, w, mask)  # warm-up: per-device set-up happens outside the capture
+    pkg.status()
+    torch.cuda.synchronize()
+    before = pkg.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = _block_products(pkg, x_static, w, mask)
+    launches = pkg.launch_count() - before
+    assert 5 <= launches <= 7, "one kernel per layer call (plus a reduction where the planner splits K)"
+    for seed in (64, 65):
+        x_new = dev(orc.Rng(seed).randn((2048, 96)), cuda)
+        x_static.copy_(x_new)
+        graph.replay()
+        torch.cuda.synchronize()
+        pkg.status()
+        want = _block_products(pkg, x_new, w, mask)
+        pkg.status()
+        assert torch.equal(y_static, want)
+    # and against the reference's sequence of separate steps, evaluated with the CPU oracle
+    xn = x_new.cpu().numpy()
+    wn = {k: v.cpu().numpy() for k, v in w.items()}
+    qkv = (orc.matmul(xn, wn["qkv"]) + wn["bqkv"]).reshape(32, 64, 3, 4, 24).transpose(2, 0, 3, 1, 4)
+    scores = orc.matmul(np.ascontiguousarray(qkv[0]), np.ascontiguousarray(qkv[1].transpose(0, 1, 3, 2)))
+    scores = scores * np.float32(24 ** -0.5) + mask.cpu().numpy()
+    e = np.exp(scores - scores.max(-1, keepdims=True), dtype=np.float32)
+    p = (e / e.sum(-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    ctx = orc.matmul(p, np.ascontiguousarray(qkv[2])).transpose(0, 2, 1, 3).reshape(2048, 96)
+    o = orc.matmul(np.ascontiguousarray(ctx), wn["out"]) + wn["bout"]
+    h = np.maximum(orc.matmul(o, wn["ff1"]) + wn["b1"], np.float32(0))
+    ref = orc.matmul(h, wn["ff2"]) + wn["b2"]
+    assert orc.scaled_error(y_static.cpu().numpy(), ref) <= 5e-5  # five layers deep
