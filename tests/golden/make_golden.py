@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ (run in the build container, where the
 reference tree and the reference CPU build oracle/_ref are present):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <reference source tree>]
 
 Outputs (small, committed):
   pytorch_matmul.npz / .bin   the reference's own PyTorch golden vectors for its matrix product and
