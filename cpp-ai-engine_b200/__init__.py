@@ -31,4 +31,4 @@ from .lib import (  # noqa: F401
     workspace_bytes,
 )
 from . import engine, lib, shard  # noqa: F401
-from .engine import Tensor, attention_scores, conv2d, conv2d_backward, linear, multi_head_attention_core, scaled_dot_product_attention, matmul, matmul_backward, ops_matmul  # noqa: F401
+from .engine import Tensor, attention_scores, conv2d, conv2d_backward, linear, multi_head_attention_core, multi_head_attention_core_backward, scaled_dot_product_attention, scaled_dot_product_attention_backward, matmul, matmul_backward, ops_matmul  # noqa: F401

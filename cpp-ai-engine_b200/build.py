@@ -10,7 +10,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libb200gemm.so"
 SOURCES = [CSRC / "gemm_sm100.cu"]
-HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "attention_kernel.cuh", CSRC / "sm100_ptx.cuh", PKG_DIR.parent / "include" / "b200_gemm.h"]
+HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "attention_kernel.cuh", CSRC / "attention_bwd_kernel.cuh", CSRC / "sm100_ptx.cuh", PKG_DIR.parent / "include" / "b200_gemm.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

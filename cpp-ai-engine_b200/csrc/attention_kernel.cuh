@@ -29,6 +29,8 @@ namespace b200 {
 
 constexpr int kAttnWorkers = 256;               // warps 1..8: two threads per query row
 constexpr int kAttnThreads = 32 + kAttnWorkers;  // warp 0: MMA issue + TMEM
+// Nine warps put three on one of the SM's four register files (16384 registers each), so a thread
+// can have 168 registers at most: a larger per-thread cap compiles but cannot be launched.
 constexpr int kAttnMaxSk = 128;
 constexpr int kAttnMaxD = 64;
 

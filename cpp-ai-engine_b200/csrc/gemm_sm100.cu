@@ -3,6 +3,7 @@
 // include/b200_gemm.h.  No CPU fallback exists: a shape the kernels cannot run is an error.
 #include "../../include/b200_gemm.h"
 #include "attention_kernel.cuh"
+#include "attention_bwd_kernel.cuh"
 #include "gemm_kernel.cuh"
 
 #include <algorithm>
@@ -1131,6 +1132,59 @@ cudaError_t launch_attention(const b200::AttnParams& p, int grid, uint32_t smem,
     b200::attention_fwd_kernel<CH><<<grid, b200::kAttnThreads, smem, stream>>>(p);
     return cudaGetLastError();
 }
+template <int CH>
+cudaError_t launch_attention_bwd(const b200::AttnBwdParams& p, int grid, uint32_t smem, cudaStream_t stream) {
+    static uint32_t attr_bytes[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > attr_bytes[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(b200::attention_bwd_kernel<CH>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_bytes[dev] = smem;
+    }
+    b200::attention_bwd_kernel<CH><<<grid, b200::kAttnThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// Shared-memory layout of the attention backward kernel; returns the bytes to request, or 0 if
+// the tiles do not fit one CTA.
+uint32_t attention_bwd_layout(b200::AttnBwdParams& p) {
+    const auto up = [](int v, int m) { return (v + m - 1) / m * m; };
+    p.sq_pad = up(p.s_q, 32);
+    p.sk_pad = up(p.s_k, 32);
+    p.dk_pad = up(p.d_k, 32);
+    p.dv_pad = up(p.d_v, 32);
+    p.dk_n = up(p.d_k, 16);
+    p.dv_n = up(p.d_v, 16);
+    p.rows_q = up(p.s_q, 8);
+    p.rows_k = up(p.s_k, 8);
+    p.sz_qa = 128u * p.dk_pad * 4u;
+    p.sz_doa = 128u * p.dv_pad * 4u;
+    p.sz_kb = static_cast<uint32_t>(p.sk_pad) * p.dk_pad * 4u;
+    p.sz_vb = static_cast<uint32_t>(p.sk_pad) * p.dv_pad * 4u;
+    p.sz_wt = static_cast<uint32_t>(p.rows_k) * p.sq_pad * 4u;
+    p.sz_ds = static_cast<uint32_t>(p.rows_q) * p.sk_pad * 4u;
+    p.sz_dst = p.sz_wt;
+    p.sz_dot = static_cast<uint32_t>(p.dv_n) * p.sq_pad * 4u;
+    p.sz_kt = static_cast<uint32_t>(p.dk_n) * p.sk_pad * 4u;
+    p.sz_qt = static_cast<uint32_t>(p.dk_n) * p.sq_pad * 4u;
+    uint32_t a = 0;  // the first two products
+    p.off_qa = a, a += 2 * p.sz_qa;
+    p.off_doa = a, a += 2 * p.sz_doa;
+    p.off_kb = a, a += 2 * p.sz_kb;
+    p.off_vb = a, a += 2 * p.sz_vb;
+    uint32_t b = 0;  // the last three, over the same bytes
+    p.off_wt = b, b += 2 * p.sz_wt;
+    p.off_ds = b, b += 2 * p.sz_ds;
+    p.off_dst = b, b += 2 * p.sz_dst;
+    p.off_dot = b, b += 2 * p.sz_dot;
+    p.off_kt = b, b += 2 * p.sz_kt;
+    p.off_qt = b, b += 2 * p.sz_qt;
+    // 16 KB of slack: an A tile with fewer than 128 rows is read past its end; 1 KB to align
+    const uint32_t total = std::max(a, b) + 16384u + 1024u;
+    return total <= 227u * 1024u ? total : 0u;
+}
 }  // namespace
 
 extern "C" {
@@ -1210,6 +1264,75 @@ int b200_attention_f32(const float* q, const float* k, const float* v, const flo
     const int64_t vs[3] = {s_k * d_v, 0, d_v}, os[3] = {s_q * d_v, 0, d_v};
     return b200_attention_f32_strided(q, k, v, mask, out, weights, batch, 1, s_q, s_k, d_k, d_v, qs, ks, vs, os,
                                       scale, precision, stream);
+}
+
+int b200_attention_backward_f32_strided(const float* q, const float* k, const float* v, const float* mask,
+                                        const float* dout, float* dq, float* dk, float* dv, int64_t batch,
+                                        int64_t heads, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                                        const int64_t q_strides[3], const int64_t k_strides[3],
+                                        const int64_t v_strides[3], const int64_t out_strides[3], float scale,
+                                        float beta, int precision, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (batch < 0 || heads <= 0 || s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
+    if (precision != B200_PRECISION_3XTF32 && precision != B200_PRECISION_TF32) return B200_EINVAL;
+    if (q_strides == nullptr || k_strides == nullptr || v_strides == nullptr || out_strides == nullptr)
+        return B200_EINVAL;
+    if (q_strides[2] < d_k || k_strides[2] < d_k || v_strides[2] < d_v || out_strides[2] < d_v) return B200_EINVAL;
+    for (int i = 0; i < 2; ++i)
+        if (q_strides[i] < 0 || k_strides[i] < 0 || v_strides[i] < 0 || out_strides[i] < 0) return B200_EINVAL;
+    if (s_q > 128 || s_k > kAttnMaxSk || d_k > kAttnMaxD || d_v > kAttnMaxD) return B200_ERANGE;
+    if (batch == 0) return B200_OK;
+    if (q == nullptr || k == nullptr || v == nullptr || dout == nullptr) return B200_EINVAL;
+    if (batch > 0x7fffffffll / heads) return B200_ERANGE;
+    AttnBwdParams p{};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.mask = mask;
+    p.dout = dout;
+    p.dq = dq;
+    p.dk = dk;
+    p.dv = dv;
+    p.q_bs = q_strides[0], p.q_hs = q_strides[1], p.q_ld = q_strides[2];
+    p.k_bs = k_strides[0], p.k_hs = k_strides[1], p.k_ld = k_strides[2];
+    p.v_bs = v_strides[0], p.v_hs = v_strides[1], p.v_ld = v_strides[2];
+    p.o_bs = out_strides[0], p.o_hs = out_strides[1], p.o_ld = out_strides[2];
+    p.batch = static_cast<int>(batch * heads);
+    p.heads = static_cast<int>(heads);
+    p.s_q = static_cast<int>(s_q);
+    p.s_k = static_cast<int>(s_k);
+    p.d_k = static_cast<int>(d_k);
+    p.d_v = static_cast<int>(d_v);
+    p.scale = scale;
+    p.beta = beta;
+    p.precision = precision;
+    p.status = st->status;
+    const uint32_t smem = attention_bwd_layout(p);
+    if (smem == 0) return B200_ERANGE;  // the tiles of this shape do not fit one CTA
+    const int grid = static_cast<int>(std::min<int64_t>(p.batch, st->sm_count));
+    cudaError_t e = cudaSuccess;
+    switch (p.sk_pad / 32) {
+        case 1: e = launch_attention_bwd<1>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        case 2: e = launch_attention_bwd<2>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        case 3: e = launch_attention_bwd<3>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+        default: e = launch_attention_bwd<4>(p, grid, smem, static_cast<cudaStream_t>(stream)); break;
+    }
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return B200_OK;
+}
+
+int b200_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
+                                const float* dout, float* dq, float* dk, float* dv, int64_t batch, int64_t s_q,
+                                int64_t s_k, int64_t d_k, int64_t d_v, float scale, float beta, int precision,
+                                void* stream) {
+    if (s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return B200_EINVAL;
+    const int64_t qs[3] = {s_q * d_k, 0, d_k}, ks[3] = {s_k * d_k, 0, d_k};
+    const int64_t vs[3] = {s_k * d_v, 0, d_v}, os[3] = {s_q * d_v, 0, d_v};
+    return b200_attention_backward_f32_strided(q, k, v, mask, dout, dq, dk, dv, batch, 1, s_q, s_k, d_k, d_v, qs, ks,
+                                               vs, os, scale, beta, precision, stream);
 }
 
 int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,

@@ -233,6 +233,80 @@ def scaled_dot_product_attention(query, key, value, mask=None, *, return_weights
     return (out, weights) if return_weights else out
 
 
+def scaled_dot_product_attention_backward(query, key, value, grad_out, mask=None, *,
+                                          precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """The gradients autograd hands query, key and value of ``scaled_dot_product_attention`` for ``grad_out``
+    (the backward of the five nodes of src/transformer.cpp:279-304), as ONE kernel that recomputes the
+    attention weights: ``(grad_query, grad_key, grad_value)``.  Raises ``RuntimeError`` (B200_ERANGE) for
+    shapes whose tiles do not fit one CTA — S = 64 with head widths up to 64 do."""
+    import math
+
+    import torch
+
+    for name, t in (("query", query), ("key", key), ("value", value), ("grad_out", grad_out)):
+        _check_operand(t, name)
+        if t.dim() < 2:
+            raise ValueError("Attention needs at least 2 dimensions (seq, d_k).")
+    d_k = query.shape[-1]
+    if key.shape[-1] != d_k:
+        raise ValueError(f"Query and key must share d_k: {tuple(query.shape)} and {tuple(key.shape)}.")
+    lead = list(query.shape[:-2])
+    if list(key.shape[:-2]) != lead or list(value.shape[:-2]) != lead or key.shape[-2] != value.shape[-2]:
+        raise ValueError("query, key and value need the same leading axes and key/value the same length")
+    s_q, s_k, d_v = query.shape[-2], key.shape[-2], value.shape[-1]
+    if list(grad_out.shape) != lead + [s_q, d_v]:
+        raise ValueError(f"grad_out must be {tuple(lead + [s_q, d_v])}, received {tuple(grad_out.shape)}.")
+    if mask is not None:
+        _check_operand(mask, "mask")
+        if list(mask.shape) != [s_q, s_k]:
+            raise ValueError("mask must be (S_q, S_k)")
+    batch = 1
+    for d in lead:
+        batch *= d
+    gq, gk, gv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+    if batch:
+        _lib.attention_backward_strided(
+            query, key, value, mask, grad_out, gq, gk, gv, batch=batch, heads=1, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
+            q_strides=(s_q * d_k, 0, d_k), k_strides=(s_k * d_k, 0, d_k), v_strides=(s_k * d_v, 0, d_v),
+            out_strides=(s_q * d_v, 0, d_v), scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+    return gq, gk, gv
+
+
+def multi_head_attention_core_backward(query, key, value, grad_merged, num_heads: int, mask=None, *,
+                                       precision: int = _lib.PRECISION_3XTF32, stream=None):
+    """Backward of ``multi_head_attention_core``: from the gradient of the merged context (B, S, d_model) to the
+    gradients of the three projections (B, S, d_model), heads addressed by strides both ways."""
+    import math
+
+    import torch
+
+    for name, t in (("query", query), ("key", key), ("value", value), ("grad_merged", grad_merged)):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32:
+            raise TypeError(f"{name} must be a float32 CUDA tensor")
+        if t.dim() != 3 or t.stride(2) != 1:
+            raise ValueError(f"{name} must be (batch, seq, d_model), dense along its last axis")
+    batch, s_q, d_model = query.shape
+    s_k = key.shape[1]
+    if num_heads <= 0 or d_model % num_heads != 0 or value.shape[2] % num_heads != 0:
+        raise ValueError("d_model must be divisible by num_heads.")
+    d_k, d_v = d_model // num_heads, value.shape[2] // num_heads
+    if list(grad_merged.shape) != [batch, s_q, num_heads * d_v]:
+        raise ValueError("grad_merged must have the shape of the merged context")
+    if mask is not None:
+        _check_operand(mask, "mask")
+    # gradients in the projections' own layout (also when those are column slices of one tensor)
+    gq, gk, gv = (torch.empty_strided(t.shape, t.stride(), dtype=torch.float32, device=t.device)
+                  for t in (query, key, value))
+    if batch:
+        _lib.attention_backward_strided(
+            query, key, value, mask, grad_merged, gq, gk, gv, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k,
+            d_v=d_v, q_strides=(query.stride(0), d_k, query.stride(1)), k_strides=(key.stride(0), d_k, key.stride(1)),
+            v_strides=(value.stride(0), d_v, value.stride(1)),
+            out_strides=(grad_merged.stride(0), d_v, grad_merged.stride(1)), scale=1.0 / math.sqrt(float(d_k)),
+            precision=precision, stream=stream)
+    return gq, gk, gv
+
+
 def multi_head_attention_core(query, key, value, num_heads: int, mask=None, *, return_weights: bool = False,
                               precision: int = _lib.PRECISION_3XTF32, stream=None):
     """The middle of ``MultiHeadAttention::forward`` (src/transformer.cpp:339-357): from the three projections

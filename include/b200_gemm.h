@@ -152,6 +152,30 @@ int b200_attention_f32_strided(const float* q, const float* k, const float* v, c
                                const int64_t k_strides[3], const int64_t v_strides[3],
                                const int64_t out_strides[3], float scale, int precision, void* stream);
 
+/* The backward pass of the attention core as ONE kernel.  The reference's autograd runs the
+ * backward of each node of scaled_dot_product_attention (src/transformer.cpp:279-304): two product
+ * backwards with materialised transposes (src/tensor_ops.cpp:570-585), the softmax backward
+ * dX_ij = y_ij (dY_ij - sum_k dY_ik y_ik) (src/tensor_ops.cpp:649-668; kernel src/cuda/kernels.cu),
+ * the scalar multiply's and the transpose's.  Here, per head, the scores are recomputed (same
+ * arithmetic as the forward kernel), and
+ *     dW = dout x v^T,  dv = W^T x dout,  dS = W o (dW - rowsum(dW o W)) * scale,
+ *     dq = dS x k,      dk = dS^T x q
+ * run as five tensor-core products around the row arithmetic; nothing of size (S_q, S_k) reaches
+ * global memory.  dq, dk, dv (any may be NULL) are addressed like q, k, v; dout like the forward's
+ * out; beta = 0 overwrites, beta = 1 accumulates (Tensor::add_grad, src/tensor.cpp:168-203).
+ * Limits: those of the forward kernel AND the tiles of a head must fit one CTA's shared memory
+ * (S = 64 with d <= 64 does; S = 128 does not): B200_ERANGE otherwise — use the separate products. */
+int b200_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
+                                const float* dout, float* dq, float* dk, float* dv, int64_t batch,
+                                int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v, float scale, float beta,
+                                int precision, void* stream);
+int b200_attention_backward_f32_strided(const float* q, const float* k, const float* v, const float* mask,
+                                        const float* dout, float* dq, float* dk, float* dv, int64_t batch,
+                                        int64_t heads, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                                        const int64_t q_strides[3], const int64_t k_strides[3],
+                                        const int64_t v_strides[3], const int64_t out_strides[3],
+                                        float scale, float beta, int precision, void* stream);
+
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials
  * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */

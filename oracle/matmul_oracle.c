@@ -275,3 +275,34 @@ void oracle_randn(oracle_rng* g, float* out, size_t n, float mean, float stddev)
         out[i] = ret * stddev + mean;
     }
 }
+
+/* Tensor::softmax over the last axis (src/tensor_ops.cpp:621-647): row maximum, expf of the
+ * difference, fp32 sum in ascending column order, division. */
+void oracle_softmax_rows_f32(const float* x, float* y, size_t rows, size_t cols) {
+    for (size_t i = 0; i < rows; ++i) {
+        const float* row = x + i * cols;
+        float* out = y + i * cols;
+        float max_v = row[0];
+        for (size_t j = 1; j < cols; ++j)
+            if (max_v < row[j]) max_v = row[j];
+        float denom = 0.0f;
+        for (size_t j = 0; j < cols; ++j) {
+            const float e = expf(row[j] - max_v);
+            out[j] = e;
+            denom += e;
+        }
+        for (size_t j = 0; j < cols; ++j) out[j] /= denom;
+    }
+}
+
+/* Its backward (src/tensor_ops.cpp:649-668): dX_ij = y_ij * (g_ij - sum_k g_ik * y_ik), the dot
+ * in fp32, ascending k, product rounded before it is added. */
+void oracle_softmax_backward_f32(const float* y, const float* g, float* dx, size_t rows, size_t cols) {
+    for (size_t i = 0; i < rows; ++i) {
+        const float* yr = y + i * cols;
+        const float* gr = g + i * cols;
+        float dot = 0.0f;
+        for (size_t j = 0; j < cols; ++j) dot += gr[j] * yr[j];
+        for (size_t j = 0; j < cols; ++j) dx[i * cols + j] = yr[j] * (gr[j] - dot);
+    }
+}

@@ -59,6 +59,11 @@ void oracle_matmul_backward_f32(const float* a, const float* b, const float* gra
 void oracle_matmul_f64(const float* a, const float* b, double* c, size_t M, size_t K, size_t N,
                        int trans_a, int trans_b, size_t lda, size_t ldb, int threads);
 
+/* Tensor::softmax over the last axis and its backward (src/tensor_ops.cpp:621-668), in the
+ * reference's operation order. */
+void oracle_softmax_rows_f32(const float* x, float* y, size_t rows, size_t cols);
+void oracle_softmax_backward_f32(const float* y, const float* g, float* dx, size_t rows, size_t cols);
+
 /* The reference's random streams: one global std::mt19937 (src/tensor.cpp:24-31) drawn
  * through std::uniform_real_distribution<float> (Tensor::rand, src/tensor.cpp:117-125) and
  * std::normal_distribution<float> (Tensor::randn, src/tensor.cpp:127-135), restated for

@@ -216,6 +216,51 @@ def conv2d_backward(x, weight, grad_out, stride: int, pad: int):
     return grad_x, grad_w, grad_b
 
 
+# --- scaled_dot_product_attention as the reference composes it ---------------------------------
+
+def softmax_rows(x: np.ndarray) -> np.ndarray:
+    """Tensor::softmax (src/tensor_ops.cpp:621-647) through the C restatement (libm's expf, like the
+    reference build; numpy's own exp differs from it in the last bit)."""
+    x = _f32(x)
+    y = np.empty_like(x)
+    oracle().oracle_softmax_rows_f32(_p(x), _p(y), _sz(x.size // x.shape[-1]), _sz(x.shape[-1]))
+    return y
+
+
+def softmax_backward(y: np.ndarray, g: np.ndarray) -> np.ndarray:
+    """dX_ij = y_ij (g_ij - sum_k g_ik y_ik) (src/tensor_ops.cpp:649-668)."""
+    y, g = _f32(y), _f32(g)
+    dx = np.empty_like(y)
+    oracle().oracle_softmax_backward_f32(_p(y), _p(g), _p(dx), _sz(y.size // y.shape[-1]), _sz(y.shape[-1]))
+    return dx
+
+
+def attention_forward(q, k, v, mask=None):
+    """src/transformer.cpp:279-304 on (lead, S, d) operands: (out, weights)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    scale = np.float32(1.0) / np.sqrt(np.float32(q.shape[-1]))
+    scores = matmul(q, np.ascontiguousarray(np.swapaxes(k, -1, -2))) * scale
+    if mask is not None:
+        scores = scores + _f32(mask)
+    w = softmax_rows(scores)
+    return matmul(w, v), w
+
+
+def attention_backward(q, k, v, mask, grad_out):
+    """The gradients autograd hands q, k, v: the product backward of W x V (src/tensor_ops.cpp:570-585),
+    the softmax backward dX_ij = y_ij (g_ij - sum_k g_ik y_ik) with its sequential fp32 dot
+    (src/tensor_ops.cpp:649-668), the scalar multiply's backward, the product backward of Q x K^T
+    and the transpose's.  Returns (out, weights, grad_q, grad_k, grad_v)."""
+    q, k, v, grad_out = _f32(q), _f32(k), _f32(v), _f32(grad_out)
+    scale = np.float32(1.0) / np.sqrt(np.float32(q.shape[-1]))
+    kt = np.ascontiguousarray(np.swapaxes(k, -1, -2))
+    out, w = attention_forward(q, k, v, mask)
+    grad_w, grad_v = matmul_backward(w, v, grad_out)
+    grad_scores = softmax_backward(w, grad_w) * scale
+    grad_q, grad_kt = matmul_backward(q, kt, grad_scores)
+    return out, w, grad_q, np.ascontiguousarray(np.swapaxes(grad_kt, -1, -2)), grad_v
+
+
 # --- the reference engine itself -------------------------------------------------------------
 
 def ref_matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
@@ -254,3 +299,20 @@ def ref_conv2d_backward(x, weight, bias, grad_out, stride: int, pad: int):
     if rc != 0:
         raise ValueError(ref().ref_last_error().decode())
     return y, gx, gw, (gb if bias is not None else None)
+
+
+def ref_attention_backward(q, k, v, mask, grad_out):
+    """The reference's own attention and autograd on (lead, S, d) operands:
+    (out, weights, grad_q, grad_k, grad_v)."""
+    q, k, v, grad_out = _f32(q), _f32(k), _f32(v), _f32(grad_out)
+    lead, s_q, d_k = q.shape
+    s_k, d_v = k.shape[1], v.shape[2]
+    out, w = np.empty((lead, s_q, d_v), np.float32), np.empty((lead, s_q, s_k), np.float32)
+    gq, gk, gv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    m = _f32(mask) if mask is not None else None
+    rc = ref().ref_attention_backward(_p(q), _p(k), _p(v), _p(m) if m is not None else None, _p(grad_out), _p(out),
+                                      _p(w), _p(gq), _p(gk), _p(gv), _sz(lead), _sz(s_q), _sz(s_k), _sz(d_k),
+                                      _sz(d_v))
+    if rc != 0:
+        raise ValueError(ref().ref_last_error().decode())
+    return out, w, gq, gk, gv

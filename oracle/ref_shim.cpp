@@ -211,4 +211,33 @@ int ref_conv2d_backward(const float* x, const float* weight, const float* bias, 
     }
 }
 
+// scaled_dot_product_attention forward and backward through the engine's own autograd
+// (src/transformer.cpp:279-304): output, attention weights and the gradients of q, k, v for an
+// explicit grad_output.  lead = number of (batch, head) matrices; mask may be null.
+int ref_attention_backward(const float* q, const float* k, const float* v, const float* mask,
+                           const float* grad_out, float* out, float* weights, float* grad_q, float* grad_k,
+                           float* grad_v, size_t lead, size_t s_q, size_t s_k, size_t d_k, size_t d_v) {
+    try {
+        Tensor Q = from_buffer(q, {lead, s_q, d_k}, true);
+        Tensor K = from_buffer(k, {lead, s_k, d_k}, true);
+        Tensor V = from_buffer(v, {lead, s_k, d_v}, true);
+        Tensor M;
+        if (mask != nullptr) M = from_buffer(mask, {s_q, s_k}, false);
+        Tensor W;
+        Tensor O = engine::nn::scaled_dot_product_attention(Q, K, V, mask != nullptr ? &M : nullptr, &W);
+        Tensor G = from_buffer(grad_out, O.shape(), false);
+        O.backward(G);
+        if (out) std::copy_n(O.data(), O.size(), out);
+        if (weights) std::copy_n(W.data(), W.size(), weights);
+        Tensor gq = Q.grad(), gk = K.grad(), gv = V.grad();
+        std::copy_n(gq.data(), gq.size(), grad_q);
+        std::copy_n(gk.data(), gk.size(), grad_k);
+        std::copy_n(gv.data(), gv.size(), grad_v);
+        return 0;
+    } catch (const std::exception& e) {
+        set_error(e.what());
+        return 1;
+    }
+}
+
 }  // extern "C"

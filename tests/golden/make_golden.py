@@ -11,7 +11,10 @@ Outputs (small, committed):
                        (tests/fixtures/conv2d_*.bin).
   reference_conv_backward.npz  the UNMODIFIED reference engine's Conv2d forward + autograd backward on
                        seeded inputs (drawn from its own generator): inputs, output and the three gradients.
-  pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward (tests/fixtures/attention*.bin).
+  pytorch_attention.npz  the reference's PyTorch golden vectors for attention forward and backward
+                       (tests/fixtures/attention*.bin).
+  reference_attention_backward.npz  the UNMODIFIED reference engine's scaled_dot_product_attention + autograd on
+                       seeded inputs: output and the three gradients (the inputs are re-drawn from the seed).
   pytorch_multihead.npz  the same for a whole MultiHeadAttention forward (tests/fixtures/multihead_attention.bin).
   pytorch_layers.bin   the Conv2d, attention and MultiHeadAttention vectors again, in the container format,
                        for the C++ host tests.
@@ -109,6 +112,19 @@ def config_inputs(name: str, rng_factory):
     raise KeyError(name)
 
 
+# (lead, s_q, s_k, d_k, d_v, causal) of the recorded attention-backward runs, inputs from seed 13
+ATTENTION_BACKWARD_CASES = {"charlm_heads": (2, 64, 64, 24, 24, True), "ragged": (3, 17, 33, 9, 20, False)}
+
+
+def attention_backward_inputs(tag: str, rng_factory):
+    lead, s_q, s_k, d_k, d_v, causal = ATTENTION_BACKWARD_CASES[tag]
+    g = rng_factory(13)
+    q, k, v = g.randn((lead, s_q, d_k)), g.randn((lead, s_k, d_k)), g.randn((lead, s_k, d_v))
+    go = g.randn((lead, s_q, d_v))
+    mask = np.triu(np.full((s_q, s_k), -1e9, np.float32), 1) if causal else None
+    return q, k, v, go, mask
+
+
 CONFIGS = ["cfg1_512", "det_200x150x120", "cfg4_relu_256", "cfg2_scores", "cfg2_shared"]
 
 
@@ -167,9 +183,19 @@ def main() -> None:
     for name in ["attention", "attention_causal"]:
         fx = read_fixture(ref_dir / "tests" / "fixtures" / f"{name}.bin")
         for key, val in fx.items():
-            if not key.startswith("grad"):
-                att[f"{name}/{key}"] = val
+            att[f"{name}/{key}"] = val
     np.savez(HERE / "pytorch_attention.npz", **att)
+
+    # 1c'. the reference engine's own attention + autograd on seeded inputs.  Only the results are
+    #      stored: the inputs are drawn again from the same seed by attention_backward_inputs()
+    #      (the oracle's generator reproduces the reference's streams bit for bit, see section 3).
+    ab = {}
+    for tag in ATTENTION_BACKWARD_CASES:
+        q, k, v, go, mask = attention_backward_inputs(tag, RefRng)
+        out, w, gq, gk, gv = orc.ref_attention_backward(q, k, v, mask, go)
+        for key, val in (("output", out), ("grad.q", gq), ("grad.k", gk), ("grad.v", gv)):
+            ab[f"{tag}/{key}"] = val
+    np.savez(HERE / "reference_attention_backward.npz", **ab)
 
     # 1d. the reference's PyTorch golden vectors for MultiHeadAttention(8, 2) forward
     #     (tests/fixtures/multihead_attention.bin, consumed by tests/test_reference.cpp:322-349):

@@ -147,3 +147,26 @@ def test_conv_restatement_against_reference_engine(orc):
         assert np.array_equal(orc.conv2d_forward(x, wt, b, stride, pad), y)
         gx2, gw2, gb2 = orc.conv2d_backward(x, wt, dy, stride, pad)
         assert np.array_equal(gx, gx2) and np.array_equal(gw, gw2) and np.array_equal(gb, gb2)
+
+
+def test_attention_restatement_against_golden(orc, golden_dir):
+    """The restatement of scaled_dot_product_attention and its backward reproduces, bit for bit, the
+    recorded results of the unmodified reference engine, and the reference's PyTorch vectors within 1e-4."""
+    import make_golden
+
+    z = np.load(golden_dir / "reference_attention_backward.npz")
+    for tag in make_golden.ATTENTION_BACKWARD_CASES:
+        q, k, v, go, mask = make_golden.attention_backward_inputs(tag, orc.Rng)
+        out, _, gq, gk, gv = orc.attention_backward(q, k, v, mask, go)
+        assert np.array_equal(out, z[f"{tag}/output"])
+        assert np.array_equal(gq, z[f"{tag}/grad.q"])
+        assert np.array_equal(gk, z[f"{tag}/grad.k"])
+        assert np.array_equal(gv, z[f"{tag}/grad.v"])
+    t = np.load(golden_dir / "pytorch_attention.npz")
+    for name in ["attention", "attention_causal"]:
+        mask = t[f"{name}/mask"] if f"{name}/mask" in t.files else None
+        flat = lambda a: a.reshape((-1,) + a.shape[-2:])  # noqa: E731
+        out, w, gq, gk, gv = orc.attention_backward(flat(t[f"{name}/q"]), flat(t[f"{name}/k"]), flat(t[f"{name}/v"]),
+                                                    mask, flat(t[f"{name}/grad_output"]))
+        for got, key in ((out, "output"), (w, "weights"), (gq, "grad.q"), (gk, "grad.k"), (gv, "grad.v")):
+            assert np.max(np.abs(got - flat(t[f"{name}/{key}"]))) <= 1e-4
