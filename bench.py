@@ -601,6 +601,23 @@ def run_engine_suite(args):
     time_layer("cfg2 attention, heads by strides (32,64,96)x3 -> (32,64,96)",
                lambda: pkg.multi_head_attention_core(qp, kp, vp, 4, mask), 1)
     time_layer("cfg2 attention, heads by permute copies + fused core", permuted, 5)
+    # backward of the attention core: one kernel against the reference's sequence (product backward of
+    # W x V, softmax backward, scale, product backward of Q x K^T, transpose) on the same GPU
+    go = torch.randn((32, 4, 64, 24), device=dev, generator=gen)
+
+    def composed_attention_backward():
+        s_ = pkg.attention_scores(q, k, 24 ** -0.5, mask)
+        w_ = torch.softmax(s_, dim=-1).reshape(128, 64, 64)
+        dw, dv_ = pkg.matmul_backward(w_, v.reshape(128, 64, 24), go.reshape(128, 64, 24))
+        ds_ = (w_ * (dw - (dw * w_).sum(-1, keepdim=True))) * (24 ** -0.5)
+        kt = k.reshape(128, 64, 24).transpose(1, 2).contiguous()
+        dq_, dkt = pkg.matmul_backward(q.reshape(128, 64, 24), kt, ds_)
+        return dq_, dkt.transpose(1, 2).contiguous(), dv_
+
+    time_layer("cfg2 attention backward fused (32,4,64,24)",
+               lambda: pkg.scaled_dot_product_attention_backward(q, k, v, go, mask), 1)
+    time_layer("cfg2 attention backward composed (scores, softmax, 4 products, softmax backward, transposes)",
+               composed_attention_backward, 13)
     # The products of one char-LM Transformer block as five layer calls, eager and replayed from a CUDA
     # graph (no host cost per launch): fused Q|K|V projection, attention on its column slices, output
     # projection, FF1 + ReLU, FF2.

@@ -785,14 +785,48 @@ Tensor conv2d(const Tensor& input_, const Tensor& weight_, const Tensor* bias, c
 
 namespace {
 
-void attention_checks(const Tensor& q, const Tensor& k, const Tensor& v) {
-    if (q.requires_grad() || k.requires_grad() || v.requires_grad()) {
-        if (g_grad_enabled) {
-            throw std::invalid_argument(
-                "The fused attention kernel is forward-only: run it on detached tensors, or train through "
-                "the separate products.");
+bool attention_tracked(const Tensor& q, const Tensor& k, const Tensor& v) {
+    return g_grad_enabled && (q.requires_grad() || k.requires_grad() || v.requires_grad());
+}
+
+// Attaches the backward of the attention core: ONE kernel that recomputes the weights and fills
+// the gradients of q, k and v (those that exist are accumulated into, Tensor::add_grad).
+void attach_attention_backward(Tensor& out, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask,
+                               bool has_mask, size_t batch, size_t heads, size_t s_q, size_t s_k, size_t d_k,
+                               size_t d_v, const int64_t (&qs)[3], const int64_t (&ks)[3], const int64_t (&vs)[3],
+                               const int64_t (&os)[3], float scale) {
+    auto qi = impl_of(q), ki = impl_of(k), vi = impl_of(v);
+    std::shared_ptr<TensorImpl> mi = has_mask ? impl_of(mask) : nullptr;
+    impl_of(out)->parents = {qi, ki, vi};
+    struct Strides {
+        int64_t q[3], k[3], v[3], o[3];
+    } st{};
+    for (int i = 0; i < 3; ++i) st.q[i] = qs[i], st.k[i] = ks[i], st.v[i] = vs[i], st.o[i] = os[i];
+    impl_of(out)->backward_fn = [qi, ki, vi, mi, st, batch, heads, s_q, s_k, d_k, d_v, scale](const Tensor& grad_out) {
+        const Tensor g = contiguous(grad_out);
+        const auto i64 = [](size_t x) { return static_cast<int64_t>(x); };
+        float* fresh[3] = {nullptr, nullptr, nullptr};
+        float* accum[3] = {nullptr, nullptr, nullptr};
+        TensorImpl* targets[3] = {qi->requires_grad ? qi.get() : nullptr, ki->requires_grad ? ki.get() : nullptr,
+                                  vi->requires_grad ? vi.get() : nullptr};
+        for (int which = 0; which < 3; ++which) {
+            if (targets[which] == nullptr) continue;
+            float beta = 0.0f;
+            float* buf = grad_buffer(*targets[which], &beta);
+            (beta == 0.0f ? fresh : accum)[which] = buf;
         }
-    }
+        auto run = [&](float* const o[3], float beta) {
+            if (o[0] == nullptr && o[1] == nullptr && o[2] == nullptr) return;
+            check_b200(b200_attention_backward_f32_strided(
+                           qi->storage.device(), ki->storage.device(), vi->storage.device(),
+                           mi ? mi->storage.device() : nullptr, impl_of(g)->storage.device(), o[0], o[1], o[2],
+                           i64(batch), i64(heads), i64(s_q), i64(s_k), i64(d_k), i64(d_v), st.q, st.k, st.v, st.o,
+                           scale, beta, current_precision(), nullptr),
+                       "attention backward");
+        };
+        run(fresh, 0.0f);
+        run(accum, 1.0f);
+    };
 }
 
 const float* mask_pointer(const Tensor* mask, size_t s_q, size_t s_k, Tensor* keep) {
@@ -816,7 +850,7 @@ Tensor scaled_dot_product_attention(const Tensor& query_, const Tensor& key_, co
         throw std::invalid_argument("Query and key must share d_k: " + query_.shape_str() + " and " +
                                     key_.shape_str() + ".");
     }
-    attention_checks(query_, key_, value_);
+    const bool tracked = attention_tracked(query_, key_, value_);
     const Tensor q = contiguous(query_), k = contiguous(key_), v = contiguous(value_);
     const std::vector<size_t> lead(q.shape().begin(), q.shape().end() - 2);
     const size_t s_q = q.shape()[q.ndim() - 2], s_k = k.shape()[k.ndim() - 2], d_v = v.shape().back();
@@ -830,7 +864,7 @@ Tensor scaled_dot_product_attention(const Tensor& query_, const Tensor& key_, co
     std::vector<size_t> out_shape = lead, w_shape = lead;
     out_shape.insert(out_shape.end(), {s_q, d_v});
     w_shape.insert(w_shape.end(), {s_q, s_k});
-    Tensor out(out_shape, 0.0f, false);
+    Tensor out(out_shape, 0.0f, tracked);
     Tensor weights = attention_weights ? Tensor(w_shape, 0.0f, false) : Tensor();
     const size_t batch = product(lead);
     if (batch == 0) return out;
@@ -843,6 +877,12 @@ Tensor scaled_dot_product_attention(const Tensor& query_, const Tensor& key_, co
                                   nullptr),
                "scaled_dot_product_attention");
     if (attention_weights) *attention_weights = weights;
+    if (tracked) {
+        const int64_t qs[3] = {i64(s_q * d_k), 0, i64(d_k)}, ks[3] = {i64(s_k * d_k), 0, i64(d_k)};
+        const int64_t vs[3] = {i64(s_k * d_v), 0, i64(d_v)}, os[3] = {i64(s_q * d_v), 0, i64(d_v)};
+        attach_attention_backward(out, q, k, v, mask_keep, mask != nullptr, batch, 1, s_q, s_k, d_k, d_v, qs, ks, vs,
+                                  os, scale);
+    }
     return out;
 }
 
@@ -863,12 +903,12 @@ Tensor multi_head_attention_core(const Tensor& query_, const Tensor& key_, const
         throw std::invalid_argument("query, key and value need the same batch, key/value the same length and "
                                     "query/key the same width.");
     }
-    attention_checks(query_, key_, value_);
+    const bool tracked = attention_tracked(query_, key_, value_);
     const Tensor q = contiguous(query_), k = contiguous(key_), v = contiguous(value_);
     const size_t s_k = k.shape()[1], d_k = d_model / num_heads, dv_model = v.shape()[2], d_v = dv_model / num_heads;
     Tensor mask_keep;
     const float* pm = mask_pointer(mask, s_q, s_k, &mask_keep);
-    Tensor out({batch, s_q, dv_model}, 0.0f, false);
+    Tensor out({batch, s_q, dv_model}, 0.0f, tracked);
     if (batch == 0) return out;
     const auto i64 = [](size_t x) { return static_cast<int64_t>(x); };
     const int64_t qs[3] = {i64(s_q * d_model), i64(d_k), i64(d_model)};
@@ -881,6 +921,10 @@ Tensor multi_head_attention_core(const Tensor& query_, const Tensor& key_, const
                                           nullptr, i64(batch), i64(num_heads), i64(s_q), i64(s_k), i64(d_k),
                                           i64(d_v), qs, ks, vs, os, scale, current_precision(), nullptr),
                "multi_head_attention_core");
+    if (tracked) {
+        attach_attention_backward(out, q, k, v, mask_keep, mask != nullptr, batch, num_heads, s_q, s_k, d_k, d_v, qs,
+                                  ks, vs, os, scale);
+    }
     return out;
 }
 

@@ -199,9 +199,11 @@ Tensor linear(const Tensor& input, const Tensor& weight, const Tensor* bias = nu
 Tensor conv2d(const Tensor& input, const Tensor& weight, const Tensor* bias, const Window2d& window);
 
 // scaled_dot_product_attention over the leading (batch, head) axes: softmax(Q K^T / sqrt(d_k) +
-// mask) V in one kernel; attention_weights, if given, receives the softmax output.  Forward
-// only: throws std::invalid_argument if an operand requires a gradient (train through the
-// separate products).  Limits: S_q, S_k <= 128 and d_k, d_v <= 64 (std::runtime_error beyond).
+// mask) V in one kernel; attention_weights, if given, receives the softmax output.  Gradients flow
+// to query, key and value through ONE backward kernel that recomputes the weights.  Limits: S_q,
+// S_k <= 128 and d_k, d_v <= 64 (std::runtime_error beyond); the backward also needs the tiles of
+// a head to fit one CTA (S = 64 with d <= 64 does, S = 128 does not: std::runtime_error from
+// backward() — train such shapes through the separate products).
 Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, const Tensor& value,
                                     const Tensor* mask = nullptr, Tensor* attention_weights = nullptr);
 

@@ -353,11 +353,20 @@ void test_layers(const std::string& golden_dir) {
         }
         check(worst <= 1e-5, name + ": attention weights sum to one per row");
     }
-    {
-        Tensor q = f.at("attention/q").detach();
+    for (const std::string name : {"attention", "attention_causal"}) {
+        const bool has_mask = f.count(name + "/mask") != 0;
+        Tensor mask = has_mask ? f.at(name + "/mask") : Tensor();
+        Tensor q = f.at(name + "/q").detach(), k = f.at(name + "/k").detach(), v = f.at(name + "/v").detach();
         q.set_requires_grad(true);
-        check_throws([&] { nn::scaled_dot_product_attention(q, f.at("attention/k"), f.at("attention/v")); },
-                     "the fused attention refuses operands that require gradients");
+        k.set_requires_grad(true);
+        v.set_requires_grad(true);
+        Tensor out = nn::scaled_dot_product_attention(q, k, v, has_mask ? &mask : nullptr);
+        const size_t before = engine::cuda::kernels_launched();
+        out.backward(f.at(name + "/grad_output"));
+        check(engine::cuda::kernels_launched() == before + 1, name + ": the backward is one kernel");
+        check(max_abs_diff(q.grad().to_vector(), f.at(name + "/grad.q").to_vector()) <= 1e-4, name + ": gradient of Q");
+        check(max_abs_diff(k.grad().to_vector(), f.at(name + "/grad.k").to_vector()) <= 1e-4, name + ": gradient of K");
+        check(max_abs_diff(v.grad().to_vector(), f.at(name + "/grad.v").to_vector()) <= 1e-4, name + ": gradient of V");
     }
 
     // MultiHeadAttention(8, 2): four Linear layers around the strided attention core
