@@ -715,7 +715,7 @@ def run_accuracy_suite(args):
             pkg.status()
             row[f"3xtf32_promote_every_{pe}"] = {"scaled_max_vs_fp64": scaled(C), "frobenius_rel_vs_fp64": fro(C),
                                                  "scaled_max_vs_cpu_loop": scaled(C, cpu)}
-        pkg.set_option("promote_every", 1)
+        pkg.set_option("promote_every", 0)  # back to automatic
         C = torch.empty((M, N), device=dev)
         pkg.gemm(A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, precision=pkg.PRECISION_TF32)
         pkg.status()

@@ -73,6 +73,7 @@ struct GemmParams {
     float alpha, beta;
     int precision;      // 0 = 3xTF32, 1 = TF32
     int promote_every;  // k-blocks per TMEM accumulation chain
+    int tf32_round;     // TF32 mode with the TMA loader: 1 = workers round the tile to nearest first
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
     // fused epilogue: out = act(alpha*acc + beta*out + bias[col] + addend[row][col])
     const float* bias;    // N values, or null
@@ -1006,8 +1007,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     float4* hi = reinterpret_cast<float4*>(stage);
                     float4* lo = reinterpret_cast<float4*>(stage + Cfg::kHalf);
                     constexpr int kN4 = Cfg::kHalf / 16;
+                    // TF32 mode without rounding: the tensor core reads the fp32 tile as it is
+                    // (it drops the low 13 mantissa bits), so the workers only pass the stage on.
+                    const int n4 = (prec3 || p.tf32_round) ? kN4 : 0;
 #pragma unroll 4
-                    for (int q = wtid; q < kN4; q += kWorkerThreads) {
+                    for (int q = wtid; q < n4; q += kWorkerThreads) {
                         const float4 x = hi[q];
                         float4 h, l;
                         tf32_split(x.x, h.x, l.x);

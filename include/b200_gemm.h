@@ -255,13 +255,18 @@ uint64_t b200_gemm_launch_count(void);
 /* Tuning knobs for benchmarking; unknown names return B200_EINVAL.
  *   "tile_n"        0 = automatic, else 32 / 64 / 128 / 256
  *   "split_k"       0 = automatic, 1 = never split, n = force n splits (needs workspace)
- *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers
+ *   "promote_every" k-blocks (32 k each) accumulated in TMEM before promotion to fp32 registers;
+ *                   0 (default) = automatic: 1 in the fp32-accurate mode, 8 in TF32 mode
  *   "force_ldg"     1 = always use the register-staged loader instead of TMA
  *   "group_m"       tile rows per scheduling band (0 = automatic: 8 for pair tiles, 16 otherwise)
  *   "tail_split"    1 (default) = when the last wave of tiles would leave most SMs idle, run its
  *                   tiles split along K in a second launch (needs workspace), 0 = never
  *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math, 0 = one
  *                   upload, one kernel, one download
+ *   "tf32_round"    B200_PRECISION_TF32 only: 1 (default) = operands are rounded to nearest TF32 first, as
+ *                   the reference's tensor-core kernel converts them (wmma::__float_to_tf32); 0 = the
+ *                   tensor core truncates them itself, which saves a pass over every tile (twice the
+ *                   operand error, biased towards zero)
  *   "pair_mode"     0 = automatic, 1 = never, 2 = whenever legal: run 256 x 256 tiles on pairs of
  *                   CTAs (tcgen05 cta_group::2) */
 int b200_gemm_set_option(const char* name, long value);
