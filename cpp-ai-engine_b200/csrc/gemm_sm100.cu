@@ -367,6 +367,7 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     const int sms = st.sm_count > 0 ? st.sm_count : 148;
     int bn = 32;
     bool pair = false;
+    const int64_t kblocks = ceil_div(K, 32);
     const bool pair_legal = pl.tma && pl.bk == 32 && M > kBM && g_opt.pair_mode != 1;
     if (g_opt.tile_n == 32 || g_opt.tile_n == 64 || g_opt.tile_n == 128 || g_opt.tile_n == 256) {
         bn = static_cast<int>(g_opt.tile_n);
@@ -389,11 +390,18 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
             const int units = cand_pair[i] ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
             const int64_t tm = ceil_div(M, rows), tn = ceil_div(N, c);
             const int64_t tiles = batch * tm * tn;
-            const int64_t waves = (tiles + units - 1) / units;
+            // A long contraction over few tiles will be split along K (below): count the parts.
+            int64_t parts = 1;
+            if (!cand_pair[i] && g_opt.split_k == 0 && kblocks >= 128 && tiles * 2 <= units) {
+                parts = std::min<int64_t>(units / tiles, kblocks / 4);
+                if (static_cast<size_t>(parts) * batch * M * N * sizeof(float) > workspace_bytes) parts = 1;
+            }
+            const int64_t items = tiles * parts;
+            const int64_t waves = (items + units - 1) / units;
             const double useful = (static_cast<double>(N) / (static_cast<double>(tn) * c)) *
                                   (static_cast<double>(M) / (static_cast<double>(tm) * rows));
-            const double score = rate[i] * useful * static_cast<double>(tiles) /
-                                 static_cast<double>(waves * units);
+            const double score = rate[i] * useful * static_cast<double>(items) /
+                                 static_cast<double>(waves * units) * (parts > 1 ? 0.9 : 1.0);
             if (score > best) {
                 best = score;
                 bn = c;

@@ -352,3 +352,32 @@ def test_host_buffer_entry_point(pkg, orc, cuda):
     out = np.full((3, 50, 30), np.nan, np.float32)
     pkg.matmul_host(a, b, out, batch=3, rows=50, inner=40, cols=30, a_batched=True, b_batched=False)
     assert orc.scaled_error(out, orc.matmul(a, b)) <= 1e-5
+
+
+def test_long_contraction_over_few_tiles_is_split(pkg, orc, cuda):
+    """512 x 512 x 8192: eight wide tiles would leave most of the GPU idle over a long k-loop, so
+    the planner picks wide tiles AND splits K over the SMs (two launches).  Exact on integers,
+    deterministic, within the K-dependent bound of the CPU loop on random inputs."""
+    import torch
+
+    M, N, K = 512, 512, 8192
+    ws_bytes = pkg.workspace_bytes(1, M, N, K)
+    assert ws_bytes >= 2 * M * N * 4, "expected a split-K plan for this shape"
+    rng = np.random.default_rng(8)
+    a = rng.integers(-4, 5, size=(M, K)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(K, N)).astype(np.float32)
+    want = orc.matmul(a, b)
+    A, B = dev(a, cuda), dev(b, cuda)
+    outs = []
+    before = pkg.launch_count()
+    for _ in range(2):
+        C = torch.empty((M, N), device=cuda)
+        gemm(pkg, cuda, A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, ws_bytes=ws_bytes)
+        outs.append(C.cpu().numpy())
+    assert pkg.launch_count() - before == 4, "product and reduction, twice"
+    assert np.array_equal(outs[0], want) and np.array_equal(outs[0], outs[1])
+    g = orc.Rng(9)
+    ar, br = g.randn((M, K)), g.randn((K, N))
+    C = torch.empty((M, N), device=cuda)
+    gemm(pkg, cuda, dev(ar, cuda), dev(br, cuda), C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, ws_bytes=ws_bytes)
+    assert orc.scaled_error(C.cpu().numpy(), orc.matmul(ar, br)) <= orc.parity_tolerance(K)
