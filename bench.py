@@ -263,6 +263,17 @@ def run_b200(args):
                               precision=precision)
         op._compute = block
 
+    if world == 1:
+        # one GPU holds every column: the plain entry point with its workspace, which lets the planner
+        # split the tiles of a mostly empty last wave along K
+        ws_bytes = pkg.workspace_bytes(1, n, n, n)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+        def whole(A_, B_, dests, col0, cols, _op=op):
+            pkg.gemm(A_, B_, _op.C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, precision=precision,
+                     workspace=ws if ws_bytes else None, workspace_bytes=ws_bytes)
+        op._compute = whole
+
     def step():
         op(A, B)
 
