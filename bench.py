@@ -340,8 +340,10 @@ def run_b200(args):
             # (profiles/gemm_tf32_kernel_pair_16384cubed_dram.md); algorithmic bytes are 3 * n^2 * 4
             "traffic": 43067955968 if (n == BIG and kfac == 3) else None,
             "algorithmic_bytes": int(3 * n * n * 4),
-            "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per launch "
-                    f"(2*M*N*K*{kfac}) / mean launch time by CUDA events; peak = cuBLAS TF32 8192^3 "
+            "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per product "
+                    f"(2*M*N*K*{kfac}) / mean time of one product by CUDA events (at one GPU a product is the "
+                    f"main launch plus the K-split launch of the last wave's tiles and their reduction; "
+                    f"traffic is the ncu figure of the single-launch plan); peak = cuBLAS TF32 8192^3 "
                     f"sustained loop measured in this run (of measured); burst {burst:.1f}",
             "useful_tflops": value, "useful_frac": value / sustained, "k_factor": kfac,
             "peak_burst": burst,
