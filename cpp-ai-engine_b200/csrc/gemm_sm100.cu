@@ -707,12 +707,15 @@ int grow(void** ptr, size_t* cap, size_t need) {
 }
 
 
-// One large product from host buffers as a 2-D wavefront of blocks: row panels of A and column
-// panels of B are uploaded alternately (A_0, B_0, A_1, B_1, ...); block C(i,j) is multiplied
-// as soon as A_i and B_j are on the device and downloaded as soon as it is done.  Uploads,
-// kernels and downloads run on three streams, so the bus works in both directions under the
-// math instead of before and after it.  Overlap needs page-locked host buffers; with pageable
-// ones the copies serialise but the result is the same.
+// One large product from host buffers as a 2-D wavefront: row panels of A and column panels of B
+// are uploaded alternately (A_0, B_0, A_1, B_1, ...).  When B_k lands, the column strip
+// C(0..k, k) = A_0..k x B_k is multiplied as ONE product; when A_k lands, the row strip
+// C(k, 0..k-1) = A_k x B_0..k-1; each strip is downloaded as soon as it is done.  Uploads, kernels
+// and downloads run on three streams, so the bus works in both directions under the math.  Thin
+// panels keep the work that only the last pair of panels unlocks small while each strip is still
+// one large launch.  The uploads are the bound: 2 GiB at the 44 GB/s this host's PCIe link gives
+// while downloads run the other way take 49 of the ~56 ms of a 16384^3 product.  Overlap needs page-locked
+// host buffers; with pageable ones the copies serialise but the result is the same.
 int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, int64_t M, int64_t K,
                    int64_t N) {
     cudaError_t e;
@@ -728,12 +731,15 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
             if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return e;
         st.pipe_ready = true;
     }
-    // panels of whole 256-row / 256-column tiles: at most 8 x 8 blocks, and no block smaller
-    // than 2048 x 2048 (64 tiles) so that every launch still fills most of the GPU
-    auto panel = [](int64_t dim) {
-        int64_t p = (dim + 7) / 8;
+    // panels of whole 256-row / 256-column tiles, at most 16 per side, none thinner than 1024
+    // 12 panels per side measured best at 16384^3 (55.6 ms; 8: 57.8, 16: 58.2, 4: 62.7): thinner
+    // strips fill the GPU worse, wider ones leave more work behind the last upload
+    const int64_t parts = g_opt.host_pipeline > 1 ? std::min<int64_t>(g_opt.host_pipeline, 16) : 12;
+    const int64_t thinnest = parts > 8 ? 1024 : 2048;
+    auto panel = [&](int64_t dim) {
+        int64_t p = (dim + parts - 1) / parts;
         p = ((p + 255) / 256) * 256;
-        return p < 2048 ? static_cast<int64_t>(2048) : p;
+        return p < thinnest ? thinnest : p;
     };
     const int64_t bm = panel(M), bn = panel(N);
     const int pm = static_cast<int>((M + bm - 1) / bm), pn = static_cast<int>((N + bn - 1) / bn);
@@ -754,17 +760,17 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
                                             static_cast<size_t>(K), cudaMemcpyHostToDevice, st.s_h2d);
         return err != cudaSuccess ? err : cudaEventRecord(st.ev_b[j], st.s_h2d);
     };
-    auto block = [&](int i, int j) -> int {
-        const int64_t r0 = i * bm, rows = std::min<int64_t>(bm, M - r0);
-        const int64_t c0 = j * bn, cols = std::min<int64_t>(bn, N - c0);
+    // C[r0 : r0 + rows, c0 : c0 + cols], once the uploads recorded in `ready` have landed
+    int strips = 0;
+    auto strip = [&](int64_t r0, int64_t rows, int64_t c0, int64_t cols, cudaEvent_t ready) -> int {
+        if (rows <= 0 || cols <= 0) return 0;
         cudaError_t err;
-        if ((err = cudaStreamWaitEvent(st.s_comp, st.ev_a[i], 0)) != cudaSuccess) return err;
-        if ((err = cudaStreamWaitEvent(st.s_comp, st.ev_b[j], 0)) != cudaSuccess) return err;
+        if ((err = cudaStreamWaitEvent(st.s_comp, ready, 0)) != cudaSuccess) return err;
         float* dest[1] = {dC + r0 * N + c0};
         int rc = gemm_impl(st, dA + r0 * K, dB + c0, dest, 1, 1, rows, cols, K, 0, 0, K, N, N, 0, 0,
                            rows * N, 1.0f, 0.0f, B200_PRECISION_3XTF32, nullptr, 0, st.s_comp);
         if (rc) return rc;
-        cudaEvent_t done = st.ev_c[i * pn + j];
+        cudaEvent_t done = st.ev_c[strips++];
         if ((err = cudaEventRecord(done, st.s_comp)) != cudaSuccess) return err;
         if ((err = cudaStreamWaitEvent(st.s_d2h, done, 0)) != cudaSuccess) return err;
         err = cudaMemcpy2DAsync(out + r0 * N + c0, static_cast<size_t>(N) * 4, dC + r0 * N + c0,
@@ -773,21 +779,23 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
         return err;
     };
 
+    // The upload stream is in order, so waiting for the newest panel covers all earlier ones.
     const int steps = std::max(pm, pn);
     for (int k = 0; k < steps; ++k) {
         if (k < pm && (e = upload_a(k)) != cudaSuccess) return e;
         if (k < pn && (e = upload_b(k)) != cudaSuccess) return e;
-        // blocks that became computable with the k-th pair of panels
-        if (k < pn)
-            for (int i = 0; i <= std::min(k, pm - 1); ++i) {
-                int rc = block(i, k);
-                if (rc) return rc;
-            }
-        if (k < pm)
-            for (int j = 0; j < std::min(k, pn); ++j) {
-                int rc = block(k, j);
-                if (rc) return rc;
-            }
+        const int rows_have = std::min(k + 1, pm), cols_before = std::min(k, pn);
+        if (k < pn) {  // column strip: every row panel uploaded so far x B_k
+            const int64_t c0 = k * bn;
+            int rc = strip(0, std::min<int64_t>(rows_have * bm, M), c0, std::min<int64_t>(bn, N - c0), st.ev_b[k]);
+            if (rc) return rc;
+        }
+        if (k < pm) {  // row strip: A_k x every column panel before B_k
+            const int64_t r0 = k * bm;
+            int rc = strip(r0, std::min<int64_t>(bm, M - r0), 0, std::min<int64_t>(cols_before * bn, N),
+                           k < pn ? st.ev_b[k] : st.ev_a[k]);
+            if (rc) return rc;
+        }
     }
     if ((e = cudaStreamSynchronize(st.s_h2d)) != cudaSuccess) return e;
     if ((e = cudaStreamSynchronize(st.s_comp)) != cudaSuccess) return e;
@@ -1440,7 +1448,8 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "tail_split")) {
         g_opt.tail_split = value ? 1 : 0;
     } else if (!std::strcmp(name, "host_pipeline")) {
-        g_opt.host_pipeline = value ? 1 : 0;
+        if (value < 0 || value > 16) return B200_EINVAL;
+        g_opt.host_pipeline = value;
     } else if (!std::strcmp(name, "tf32_round")) {
         g_opt.tf32_round = value ? 1 : 0;
     } else if (!std::strcmp(name, "pair_mode")) {

@@ -261,8 +261,9 @@ uint64_t b200_gemm_launch_count(void);
  *   "group_m"       tile rows per scheduling band (0 = automatic: 8 for pair tiles, 16 otherwise)
  *   "tail_split"    1 (default) = when the last wave of tiles would leave most SMs idle, run its
  *                   tiles split along K in a second launch (needs workspace), 0 = never
- *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math, 0 = one
- *                   upload, one kernel, one download
+ *   "host_pipeline" 1 (default) = b200_matmul_f32_host overlaps transfers and math (12 panels per
+ *                   side), 2..16 = the same with that many panels, 0 = one upload, one kernel,
+ *                   one download
  *   "tf32_round"    B200_PRECISION_TF32 only: 1 (default) = operands are rounded to nearest TF32 first, as
  *                   the reference's tensor-core kernel converts them (wmma::__float_to_tf32); 0 = the
  *                   tensor core truncates them itself, which saves a pass over every tile (twice the
