@@ -48,6 +48,8 @@ SHAPES = [
     (1, 130, 6, 6, 70, 1, 1, 0),     # 1x1 convolution, more than 128 input channels
     (2, 4, 7, 9, 3, 2, 3, 1),        # stride larger than the window: some pixels get no gradient
     (2, 3, 8, 8, 150, 3, 1, 1),      # more than 128 output channels (two row tiles of the weight gradient)
+    (1, 6, 5, 5, 460, 3, 1, 1),      # outC*kH*kW = 4140: the input gradient's gather leaves the tables
+    (1, 520, 5, 5, 12, 3, 1, 1),     # C*kH*kW = 4680 columns in the weight gradient
 ]
 
 

@@ -56,6 +56,7 @@ def test_pytorch_golden_conv2d(pkg, cuda, golden_dir):
     (3, 5, 17, 13, 7, 3, 2, 0),      # odd everything, stride 2
     (2, 3, 9, 9, 40, 5, 1, 2),       # 5x5 window, more channels than a 32-wide tile
     (1, 130, 6, 6, 70, 1, 1, 0),     # 1x1 convolution, K > 128
+    (1, 520, 5, 5, 12, 3, 1, 1),     # K = 4680: past the per-CTA gather tables, the division path
 ])
 @pytest.mark.parametrize("relu", [False, True])
 def test_against_reference_construction(pkg, orc, cuda, shape, relu):
