@@ -57,6 +57,7 @@ def test_recorded_reference_engine_gradients(pkg, orc, cuda, golden_dir):
     ((5,), 17, 33, 9, 20),        # nothing aligned, s_q != s_k, d_k != d_v
     ((2,), 40, 72, 16, 8),        # three 32-column groups of keys
     ((4,), 8, 128, 32, 32),       # few queries over the longest key axis
+    ((7, 61), 16, 24, 8, 8),      # 427 heads: every CTA walks several heads
     ((), 1, 1, 1, 1),
 ])
 @pytest.mark.parametrize("causal", [False, True])

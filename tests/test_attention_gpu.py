@@ -47,6 +47,7 @@ def test_pytorch_golden_attention(pkg, cuda, golden_dir):
     ((2, 3), 5, 5, 4, 4),         # the reference's fixture shape
     ((3,), 128, 128, 64, 64),     # the kernel's limits
     ((5,), 17, 33, 9, 20),        # nothing aligned, s_q != s_k, d_k != d_v
+    ((7, 61), 16, 24, 8, 8),      # 427 heads: every CTA walks several heads
     ((), 1, 1, 1, 1),
 ])
 @pytest.mark.parametrize("causal", [False, True])
