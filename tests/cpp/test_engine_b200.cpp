@@ -12,6 +12,7 @@
 
 #include "../../oracle/matmul_oracle.h"
 
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <functional>
@@ -420,6 +421,37 @@ void test_layers(const std::string& golden_dir) {
     check_throws([&] { nn::linear(Tensor({4, 95}), w); }, "linear with a wrong input width throws");
 }
 
+// Informational: what one engine-sized product costs a C++ caller, back to back (no result is
+// read in between, so launches queue up behind each other like in a training step).
+void report_call_cost() {
+    section("Cost per call from C++ (informational)");
+    engine::manual_seed(31);
+    Tensor x = Tensor::randn({2048, 96}), w = Tensor::rand({96, 384}, -0.1f, 0.1f);
+    Tensor b = Tensor::randn({384});
+    for (int i = 0; i < 20; ++i) x.matmul(w);
+    engine::cuda::synchronize();
+    const int reps = 500;
+    auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < reps; ++i) x.matmul(w);
+    auto t1 = std::chrono::steady_clock::now();
+    engine::cuda::synchronize();
+    auto t2 = std::chrono::steady_clock::now();
+    const double issue_us = std::chrono::duration<double, std::micro>(t1 - t0).count() / reps;
+    const double total_us = std::chrono::duration<double, std::micro>(t2 - t0).count() / reps;
+    std::cout << "  Tensor::matmul (2048 x 96) x (96 x 384): " << issue_us << " us of host time per call, " << total_us
+              << " us per call until the device is idle\n";
+    for (int i = 0; i < 20; ++i) engine::nn::linear(x, w, &b, true);
+    engine::cuda::synchronize();
+    t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < reps; ++i) engine::nn::linear(x, w, &b, true);
+    t1 = std::chrono::steady_clock::now();
+    engine::cuda::synchronize();
+    t2 = std::chrono::steady_clock::now();
+    std::cout << "  nn::linear with bias and ReLU, same shape: "
+              << std::chrono::duration<double, std::micro>(t1 - t0).count() / reps << " us of host time per call, "
+              << std::chrono::duration<double, std::micro>(t2 - t0).count() / reps << " us per call until the device is idle\n";
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -436,6 +468,7 @@ int main(int argc, char** argv) {
         test_residency_and_seam();
         test_reduced_precision_is_opt_in();
         test_layers(golden_dir);
+        report_call_cost();
         engine::cuda::check_device_status();
     } catch (const std::exception& e) {
         std::cout << "EXCEPTION: " << e.what() << "\n";
