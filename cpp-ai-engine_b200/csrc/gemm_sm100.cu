@@ -367,19 +367,28 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     const int sms = st.sm_count > 0 ? st.sm_count : 148;
     int bn = 32;
     bool pair = false;
+    int auto_parts = 0;  // K-split chosen together with the tile (0: tile forced by option)
     const int64_t kblocks = ceil_div(K, 32);
     const bool pair_legal = pl.tma && pl.bk == 32 && M > kBM && g_opt.pair_mode != 1;
     if (g_opt.tile_n == 32 || g_opt.tile_n == 64 || g_opt.tile_n == 128 || g_opt.tile_n == 256) {
         bn = static_cast<int>(g_opt.tile_n);
         pair = pair_legal && bn == 256 && g_opt.pair_mode == 2;
     } else {
-        // Score = measured relative rate of the tile shape (wider MMAs amortise the A-operand
-        // fetches; CTA pairs also halve each CTA's share of B) x the useful fraction of the
-        // tile x how full the last wave of tiles is.  Narrow products get narrow tiles instead
-        // of padding (N = 8, 10, 16, 24 run 32 wide).
+        // Time model, fitted to CUDA-graph replays of 256^3 ... 4096^3 and the engine's shapes on a
+        // B200 (microseconds):
+        //     T = launch + waves x (item(tile) + k-blocks per item x t(tile))  [+ reduction if K is split]
+        // t is what one k-block of 32 costs a CTA (or CTA pair) — latency-bound near 1 us for the
+        // narrow tiles, the tensor pipe for the wide ones — `item` the pipeline fill and the store
+        // of one tile, and a K-split adds its second kernel: 1.7 us + 0.47 us per MB of partials
+        // read and written.  For products of many waves this is the throughput ranking
+        // (pair > 256 > 128 > 64 > 32 per column); for engine-sized ones it weighs a shorter
+        // k-loop on more SMs against the reduction it costs.  Narrow products get narrow tiles
+        // instead of padding (N = 8, 10, 16, 24 run 32 wide).
         const int cand[5] = {256, 256, 128, 64, 32};
         const bool cand_pair[5] = {true, false, false, false, false};
-        const double rate[5] = {1.30, 1.0, 0.68, 0.40, 0.22};
+        const double t_kb[5] = {1.37, 1.63, 1.17, 1.06, 1.06};
+        const double item_us[5] = {7.5, 6.7, 4.2, 2.5, 2.0};
+        constexpr double kLaunchUs = 3.5;
         double best = -1.0;
         for (int i = 0; i < 5; ++i) {
             const int c = cand[i];
@@ -390,22 +399,35 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
             const int units = cand_pair[i] ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
             const int64_t tm = ceil_div(M, rows), tn = ceil_div(N, c);
             const int64_t tiles = batch * tm * tn;
-            // A long contraction over few tiles will be split along K (below): count the parts.
+            auto time_of = [&](int64_t parts) {
+                const int64_t items = tiles * parts;
+                const int64_t waves = (items + units - 1) / units;
+                const int64_t kb_item = (kblocks + parts - 1) / parts;
+                double t = kLaunchUs + static_cast<double>(waves) *
+                                           (item_us[i] + static_cast<double>(kb_item) * t_kb[i]);
+                if (parts > 1)
+                    t += 1.7 + 0.47e-6 * static_cast<double>(parts + 1) * static_cast<double>(batch) *
+                                   static_cast<double>(M) * static_cast<double>(N) * 4.0;
+                return t;
+            };
             int64_t parts = 1;
-            if (!cand_pair[i] && g_opt.split_k == 0 && kblocks >= 128 && tiles * 2 <= units) {
-                parts = std::min<int64_t>(units / tiles, kblocks / 4);
-                if (static_cast<size_t>(parts) * batch * M * N * sizeof(float) > workspace_bytes) parts = 1;
+            double t = time_of(1);
+            // deterministic split-K: few tiles, a k-loop worth cutting, room for the partials
+            if (!cand_pair[i] && g_opt.split_k == 0 && tiles * 2 <= units && kblocks >= 8) {
+                int64_t p2 = std::min<int64_t>(units / tiles, kblocks / 4);
+                const int64_t per = (kblocks + p2 - 1) / p2;
+                p2 = (kblocks + per - 1) / per;
+                if (p2 > 1 && static_cast<size_t>(p2) * batch * M * N * sizeof(float) <= workspace_bytes &&
+                    time_of(p2) < t) {
+                    parts = p2;
+                    t = time_of(p2);
+                }
             }
-            const int64_t items = tiles * parts;
-            const int64_t waves = (items + units - 1) / units;
-            const double useful = (static_cast<double>(N) / (static_cast<double>(tn) * c)) *
-                                  (static_cast<double>(M) / (static_cast<double>(tm) * rows));
-            const double score = rate[i] * useful * static_cast<double>(items) /
-                                 static_cast<double>(waves * units) * (parts > 1 ? 0.9 : 1.0);
-            if (score > best) {
-                best = score;
+            if (best < 0.0 || t < best) {
+                best = t;
                 bn = c;
                 pair = cand_pair[i];
+                auto_parts = static_cast<int>(parts);
             }
         }
     }
@@ -422,6 +444,8 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     int want = 1;
     if (g_opt.split_k > 1 && !pl.pair) {
         want = static_cast<int>(g_opt.split_k);
+    } else if (g_opt.split_k == 0 && auto_parts > 0) {
+        want = auto_parts;
     } else if (g_opt.split_k == 0 && !pl.pair && tiles * 2 <= sms && pl.kblocks >= 8) {
         want = static_cast<int>(sms / tiles);
         if (want > pl.kblocks / 4) want = pl.kblocks / 4;

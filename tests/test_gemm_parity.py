@@ -212,12 +212,14 @@ def test_pair_and_single_kernels_agree_bitwise(pkg, orc, cuda):
     outs = []
     for mode in (1, 2):
         pkg.set_option("pair_mode", mode)
+        pkg.set_option("split_k", 1)  # no K-split: its reduction adds the parts in another order
         try:
             C = torch.empty((M, N), device=cuda)
             gemm(pkg, cuda, A, B, C, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N)
             outs.append(C)
         finally:
             pkg.set_option("pair_mode", 0)
+            pkg.set_option("split_k", 0)
     assert torch.equal(outs[0], outs[1])
 
 
