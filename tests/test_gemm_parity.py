@@ -356,6 +356,31 @@ def test_host_buffer_entry_point(pkg, orc, cuda):
     assert orc.scaled_error(out, orc.matmul(a, b)) <= 1e-5
 
 
+@pytest.mark.parametrize("M,K,N", [(4352, 640, 4608), (4096, 512, 9472)])
+def test_host_buffer_entry_point_pipelined(pkg, orc, cuda, M, K, N):
+    """Large products from host buffers run as a wavefront of row and column strips that overlaps
+    uploads, kernels and downloads: every element of the result must still be the plain product
+    (sampled rows against the CPU loop, every column; all of it finite and written), with panel
+    counts that differ between rows and columns and panels that do not divide the matrix."""
+    rng = np.random.default_rng(20)
+    a = rng.standard_normal((M, K), dtype=np.float32)
+    b = rng.standard_normal((K, N), dtype=np.float32)
+    out = np.full((M, N), np.nan, np.float32)
+    pkg.matmul_host(a, b, out, batch=1, rows=M, inner=K, cols=N, a_batched=False, b_batched=False)
+    assert np.isfinite(out).all(), "a block of the result was never written"
+    rows = np.unique(np.concatenate([np.arange(0, M, 173), [M - 1, 1023, 1024, 1535, 1536, 2047, 2048]]))
+    want = orc.matmul(np.ascontiguousarray(a[rows]), b)
+    assert orc.scaled_error(out[rows], want) <= orc.parity_tolerance(K)
+    for panels in (3, 16, 0):  # other panel counts, and no pipelining at all: the same bits
+        pkg.set_option("host_pipeline", panels)
+        try:
+            again = np.full((M, N), np.nan, np.float32)
+            pkg.matmul_host(a, b, again, batch=1, rows=M, inner=K, cols=N, a_batched=False, b_batched=False)
+        finally:
+            pkg.set_option("host_pipeline", 1)
+        assert orc.scaled_error(again, out) <= orc.parity_tolerance(K)
+
+
 def test_long_contraction_over_few_tiles_is_split(pkg, orc, cuda):
     """512 x 512 x 8192: eight wide tiles would leave most of the GPU idle over a long k-loop, so
     the planner picks wide tiles AND splits K over the SMs (two launches).  Exact on integers,
