@@ -129,3 +129,20 @@ def test_limits_are_refused_not_faked(pkg, cuda):
         pkg.scaled_dot_product_attention_backward(big, big, big, big)
     with pytest.raises(ValueError):
         pkg.scaled_dot_product_attention_backward(big, big, big, torch.zeros((2, 128, 32), device=cuda))
+
+
+def test_tf32_mode_is_coarser_but_close(pkg, orc, cuda):
+    """The opt-in single-product TF32 mode of the forward and backward attention kernels: same code path
+    without the correction products — about three decimal digits."""
+    g = orc.Rng(83)
+    lead, s, d = 6, 64, 24
+    q, k, v, go = g.randn((lead, s, d)), g.randn((lead, s, d)), g.randn((lead, s, d)), g.randn((lead, s, d))
+    out_want, _, want_q, want_k, want_v = orc.attention_backward(q, k, v, None, go)
+    out = pkg.scaled_dot_product_attention(dev(q, cuda), dev(k, cuda), dev(v, cuda), precision=pkg.PRECISION_TF32)
+    gq, gk, gv = pkg.scaled_dot_product_attention_backward(dev(q, cuda), dev(k, cuda), dev(v, cuda), dev(go, cuda),
+                                                           precision=pkg.PRECISION_TF32)
+    pkg.status()
+    e_out = orc.scaled_error(out.cpu().numpy(), out_want)
+    assert 1e-6 < e_out <= 2e-2
+    for got, want in ((gq, want_q), (gk, want_k), (gv, want_v)):
+        assert orc.scaled_error(got.cpu().numpy(), want) <= 5e-2

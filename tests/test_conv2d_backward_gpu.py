@@ -135,3 +135,23 @@ def test_argument_errors(pkg, cuda):
         pkg.conv2d_backward(x, torch.zeros((4, 2, 3, 3), device=cuda), torch.zeros((2, 4, 6, 6), device=cuda))
     with pytest.raises(ValueError):
         pkg.conv2d_backward(x, w, torch.zeros((2, 4, 6, 6), device=cuda), stride=0)
+
+
+def test_tf32_mode_is_coarser_but_close(pkg, orc, cuda):
+    """The opt-in TF32 mode of the convolution kernels (forward and the three gradients)."""
+    n, c, h, w, out_c, k = 8, 8, 14, 14, 16, 3
+    g = orc.Rng(54)
+    x, wt, b = g.rand((n, c, h, w), 0.0, 1.0), g.rand((out_c, c, k, k), -0.3, 0.3), g.randn((out_c,))
+    dy = g.randn((n, out_c, h, w))
+    want_y = orc.conv2d_forward(x, wt, b, 1, 1)
+    want = orc.conv2d_backward(x, wt, dy, 1, 1)
+    y = pkg.conv2d(dev(x, cuda), dev(wt, cuda), dev(b, cuda), stride=1, padding=1, precision=pkg.PRECISION_TF32)
+    got = pkg.conv2d_backward(dev(x, cuda), dev(wt, cuda), dev(dy, cuda), stride=1, padding=1,
+                              precision=pkg.PRECISION_TF32)
+    pkg.status()
+    e = orc.scaled_error(y.cpu().numpy(), want_y)
+    assert 1e-6 < e <= 4.0 * np.sqrt(c * k * k) * 2.0 ** -11
+    positions = n * h * w
+    assert orc.scaled_error(got[0].cpu().numpy(), want[0]) <= 4.0 * np.sqrt(out_c * k * k) * 2.0 ** -11 * 4
+    assert orc.scaled_error(got[1].cpu().numpy(), want[1]) <= 4.0 * np.sqrt(positions) * 2.0 ** -11 * 4
+    assert orc.scaled_error(got[2].cpu().numpy(), want[2]) <= 4.0 * np.sqrt(positions) * 2.0 ** -11 * 4
