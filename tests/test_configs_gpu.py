@@ -153,3 +153,40 @@ def test_large_square_properties_4096(pkg, orc, cuda):
     pkg.gemm(A, B, C2, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, alpha=2.0)
     pkg.status()
     assert torch.equal(C2, 2.0 * C)
+
+
+def test_largest_config_16384(pkg, orc, cuda):
+    """Configuration 5 at its full size, 16384^3 with N(0, 1/K) inputs (3 GiB on the device): sampled rows
+    against the CPU loop (rows are independent there, so these are the rows of the full product) and against
+    fp64, run-to-run bit-identity, and the plan with the K-split last wave against the plan without it."""
+    import torch
+
+    n = 16384
+    gen = torch.Generator(device=cuda).manual_seed(1)
+    A = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
+    B = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
+    C = torch.empty((n, n), device=cuda)
+    pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n)
+    pkg.status()
+    rows = torch.arange(7, n, 683, device=cuda)  # 24 rows
+    got = C[rows].cpu().numpy()
+    b_host = B.cpu().numpy()
+    want = orc.matmul(A[rows].cpu().numpy(), b_host)
+    assert orc.scaled_error(got, want) <= orc.parity_tolerance(n)
+    ref64 = (A[rows].double() @ B.double()).cpu().numpy()
+    err_gpu, err_cpu = orc.scaled_error(got, ref64), orc.scaled_error(want, ref64)
+    assert err_gpu <= 1e-6 and err_gpu <= err_cpu, (err_gpu, err_cpu)
+    del b_host, want, ref64
+    first = C[rows].clone()
+    C.zero_()
+    pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n)
+    pkg.status()
+    assert torch.equal(C[rows], first)
+    ws_bytes = pkg.workspace_bytes(1, n, n, n)
+    if ws_bytes:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda)
+        keep = C[::509].clone()
+        C.zero_()
+        pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, workspace=ws, workspace_bytes=ws_bytes)
+        pkg.status()
+        assert orc.scaled_error(C[::509].cpu().numpy(), keep.cpu().numpy()) <= 1e-5
