@@ -211,7 +211,7 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
     constexpr int kPer = kUnits / kWorkerThreads;
     static_assert(kUnits % kWorkerThreads == 0, "tile does not divide over the workers");
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             int r, c;
@@ -248,7 +248,7 @@ __device__ __forceinline__ void ldg_split_store(const float* __restrict__ base, 
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             int r, c;
@@ -286,7 +286,7 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
     const int ohw = p.cv_oh * p.cv_ow;
     const int khw = p.cv_kh * p.cv_kw;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit % kBM, c = unit / kBM;
@@ -296,7 +296,7 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
                 const int img = gr / ohw, pix = gr - img * ohw;
                 const int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
                 const int ih0 = oh * p.cv_stride - p.cv_pad, iw0 = ow * p.cv_stride - p.cv_pad;
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int gk = k0 + c * 4 + e;
                     if (gk < p.K) {
@@ -313,7 +313,7 @@ __device__ __forceinline__ void conv_gather_split_store(const GemmParams& p, int
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit % kBM, c = unit / kBM;
@@ -372,7 +372,7 @@ __device__ __forceinline__ void conv_table_gather_split_store(const float* __res
     static_assert(kWorkerThreads % kBM == 0, "a worker keeps one tile row");
     const int r = wtid % kBM;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int c = wtid / kBM + u * (kWorkerThreads / kBM);
             const int gk = k0 + c * 4;
@@ -382,7 +382,7 @@ __device__ __forceinline__ void conv_table_gather_split_store(const float* __res
                 const uint4 kd = *reinterpret_cast<const uint4*>(kdelta + gk);
                 const int ko4[4] = {ko.x, ko.y, ko.z, ko.w};
                 const uint32_t kd4[4] = {kd.x, kd.y, kd.z, kd.w};
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const uint32_t ty = static_cast<uint32_t>(row.y + static_cast<int>(kd4[e] >> 16));
                     const uint32_t tx = static_cast<uint32_t>(row.x + static_cast<int>(kd4[e] & 0xffffu));
@@ -393,7 +393,7 @@ __device__ __forceinline__ void conv_table_gather_split_store(const float* __res
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             store_unit_split(hi, lo, want_lo, r, wtid / kBM + u * (kWorkerThreads / kBM), v[u]);
         }
@@ -415,7 +415,7 @@ __device__ __forceinline__ void conv_dy_rows_split_store(const GemmParams& p, in
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int ohw = p.cv_oh * p.cv_ow;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
@@ -429,7 +429,7 @@ __device__ __forceinline__ void conv_dy_rows_split_store(const GemmParams& p, in
                     x4[0] = t.x, x4[1] = t.y, x4[2] = t.z, x4[3] = t.w;
                 } else {
                     int ii = img, ss = sp;
-    #pragma unroll
+#pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         if (m0 + e < p.K) x4[e] = __ldg(p.A + ((long long)ii * p.M + o) * ohw + ss);
                         if (++ss == ohw) ss = 0, ++ii;
@@ -440,7 +440,7 @@ __device__ __forceinline__ void conv_dy_rows_split_store(const GemmParams& p, in
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
@@ -458,7 +458,7 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
     constexpr int kPer = ROWS * 8 / kWorkerThreads;
     const int ohw = p.cv_oh * p.cv_ow, khw = p.cv_kh * p.cv_kw;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
@@ -466,7 +466,7 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
             float x4[4] = {0.f, 0.f, 0.f, 0.f};
             if (kc == p.cv_ones_col) {
                 // the bias gradient rides along as one more column of the column matrix: dOut^T x 1
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e) x4[e] = (m0 + e < p.K) ? 1.0f : 0.0f;
             } else if (kc < p.N && m0 < p.K) {
                 const int ci = kc / khw, rem = kc - ci * khw;
@@ -474,7 +474,7 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
                 int img = m0 / ohw;
                 const int pix = m0 - img * ohw;
                 int oh = pix / p.cv_ow, ow = pix - oh * p.cv_ow;
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (m0 + e < p.K) {
                         const int ih = oh * p.cv_stride - p.cv_pad + kh, iw = ow * p.cv_stride - p.cv_pad + kw;
@@ -491,7 +491,7 @@ __device__ __forceinline__ void conv_cols_T_split_store(const GemmParams& p, int
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
@@ -512,7 +512,7 @@ __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, 
     constexpr int kPer = kBM * 8 / kWorkerThreads;
     const int hw = p.cv_h * p.cv_w, khw = p.cv_kh * p.cv_kw;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit % kBM, c = unit / kBM;
@@ -521,7 +521,7 @@ __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, 
             if (gr < p.M) {
                 const int img = gr / hw, pix = gr - img * hw;
                 const int ih = pix / p.cv_w, iw = pix - ih * p.cv_w;
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int gk = k0 + c * 4 + e;
                     if (gk < p.K) {
@@ -543,7 +543,7 @@ __device__ __forceinline__ void conv_dx_gather_split_store(const GemmParams& p, 
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             store_unit_split(hi, lo, want_lo, unit % kBM, unit / kBM, v[u]);
@@ -559,7 +559,7 @@ __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, i
     constexpr int kPer = ROWS * 8 / kWorkerThreads;
     const int khw = p.cv_kh * p.cv_kw;
     if constexpr (kLoad) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
@@ -568,7 +568,7 @@ __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, i
             if (ci < p.N) {
                 int gk = k0 + c * 4;
                 int o = gk / khw, q = gk - o * khw;
-    #pragma unroll
+#pragma unroll
                 for (int e = 0; e < 4; ++e, ++gk) {
                     if (gk < p.K) x4[e] = __ldg(p.B + ((long long)o * p.cv_c + ci) * khw + q);
                     if (++q == khw) q = 0, ++o;
@@ -578,7 +578,7 @@ __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, i
         }
     }
     if constexpr (kStore) {
-    #pragma unroll
+#pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int unit = wtid + u * kWorkerThreads;
             const int r = unit >> 3, c = unit & 7;
