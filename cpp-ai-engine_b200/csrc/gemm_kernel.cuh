@@ -1112,6 +1112,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const int n_out = split_out ? 1 : p.n_dest;
                 const bool fuse = !split_out && (p.bias != nullptr || p.addend != nullptr);
                 const bool relu = !split_out && p.relu != 0;
+                const bool plain = n_out == 1 && !fuse && !relu && beta == 0.f && vec;
                 // compact: element (row, col) of tail tile t lives at
                 //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
@@ -1132,7 +1133,25 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                     __syncwarp();
                     const int col = col_base + g * 32 + chunk * 4;
-                    if (chunk < kChunks && col < p.N) {
+                    if (chunk < kChunks && col + 3 < p.N && plain) {
+                        // The common store — one destination (C or the split-K partials), nothing
+                        // fused, whole 16-byte chunks —
+                        // apart from the general one below: a small product is one tile per CTA and
+                        // fetches every instruction it executes cold, so the path it walks is short.
+                        float* dst0 = (split_out ? p.partial : p.dest[0]) + base_off + col;
+#pragma unroll 1
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + sub_row;
+                            const int row = row_base + rr;
+                            if (row >= p.M) continue;
+                            float4 v = tile[rr * 8 + (chunk ^ (rr & 7))];
+                            v.x *= alpha;
+                            v.y *= alpha;
+                            v.z *= alpha;
+                            v.w *= alpha;
+                            *reinterpret_cast<float4*>(dst0 + (long long)row * ld_out) = v;
+                        }
+                    } else if (chunk < kChunks && col < p.N) {
                         // Not unrolled on purpose: 32 copies of the store path (4 column groups x
                         // 8 row groups) made the kernel 20 % slower at 4096^3 — the k-loop's
                         // code no longer stayed in the instruction cache.
