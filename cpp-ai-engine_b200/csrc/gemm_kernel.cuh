@@ -72,6 +72,9 @@ struct GemmParams {
     int transA, transB;
     float alpha, beta;
     int precision;      // 0 = 3xTF32, 1 = TF32
+    // Multipliers that replace the scheduler's integer divisions (fast_div below): by split_k, by
+    // the tiles of one matrix, by the tiles of one band, by the rows of a full band and of the last.
+    unsigned long long fd_split, fd_tiles, fd_band, fd_rows, fd_rows_last;
     int promote_every;  // k-blocks per TMEM accumulation chain
     int tf32_round;     // TF32 mode with the TMA loader: 1 = workers round the tile to nearest first
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
@@ -123,23 +126,44 @@ struct Work {
     int tile;  // linear tile index (batch included)
 };
 
+// n / d for 0 <= n < 2^31 as one 64 x 64 -> high-64 multiply by m = ceil(2^64 / d), exact for every
+// 32-bit n (d = 1 is stored as m = 0).  The tile scheduler runs once per tile in three warps of
+// every CTA; a small product executes it cold, and a hardware-free division is ~20 instructions.
+__host__ __device__ inline unsigned long long fast_div_magic(int d) {
+    return d <= 1 ? 0ull : (~0ull) / static_cast<unsigned long long>(d) + 1ull;
+}
+__device__ __forceinline__ int fast_div(int n, unsigned long long m) {
+    return m ? static_cast<int>(__umul64hi(m, static_cast<unsigned long long>(static_cast<unsigned>(n)))) : n;
+}
+
+// Fills the multipliers from split_k, tiles_m, tiles_n and group_m (host side, before a launch).
+inline void fill_schedule(GemmParams& p) {
+    const int rows_last = p.tiles_m % p.group_m;
+    p.fd_split = fast_div_magic(p.split_k);
+    p.fd_tiles = fast_div_magic(p.tiles_m * p.tiles_n);
+    p.fd_band = fast_div_magic(p.group_m * p.tiles_n);
+    p.fd_rows = fast_div_magic(p.tiles_m < p.group_m ? p.tiles_m : p.group_m);
+    p.fd_rows_last = fast_div_magic(rows_last ? rows_last : p.group_m);
+}
+
 __device__ __forceinline__ Work decode_work(const GemmParams& p, int w) {
     Work r;
-    r.sp = w % p.split_k;
-    int t = w / p.split_k + p.tile_offset;
+    const int q = fast_div(w, p.fd_split);
+    r.sp = w - q * p.split_k;
+    int t = q + p.tile_offset;
     r.tile = t;
     const int tiles = p.tiles_m * p.tiles_n;
-    r.b = t / tiles;
+    r.b = fast_div(t, p.fd_tiles);
     t -= r.b * tiles;
     // Tiles are walked in bands of group_m tile-rows so that the CTAs running at one time
     // cover a near-square patch of C and share A and B tiles through L2.
     const int per_group = p.group_m * p.tiles_n;
-    const int g = t / per_group;
+    const int g = fast_div(t, p.fd_band);
     const int first_m = g * p.group_m;
     const int gsize = min(p.tiles_m - first_m, p.group_m);
     const int in_g = t - g * per_group;
-    r.mt = first_m + in_g % gsize;
-    r.nt = in_g / gsize;
+    r.nt = fast_div(in_g, first_m + p.group_m <= p.tiles_m ? p.fd_rows : p.fd_rows_last);
+    r.mt = first_m + in_g - r.nt * gsize;
     r.kb0 = r.sp * p.kb_per_split;
     r.kb1 = min(p.kblocks, r.kb0 + p.kb_per_split);
     return r;
@@ -1270,6 +1294,7 @@ __global__ void tail_reduce_kernel(const GemmParams p, int tile_rows, int bn) {
     const int slab = blockIdx.x & 7;
     GemmParams q = p;
     q.split_k = 1;
+    q.fd_split = 0;  // the multiplier of a division by one
     const Work wk = decode_work(q, tl);  // tile_offset is applied inside
     const int rows_per = tile_rows / 8;
     const int chunks = bn / 4;

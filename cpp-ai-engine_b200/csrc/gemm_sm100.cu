@@ -173,9 +173,11 @@ bool tma_legal(const float* base, int64_t ld, int64_t batch_stride, int64_t batc
 }
 
 template <int BN, int BK, bool kTma>
-int launch_cfg(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mb, int grid,
+int launch_cfg(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int grid,
                cudaStream_t stream) {
     using Cfg = TileCfg<BN, BK>;
+    GemmParams p = params;
+    fill_schedule(p);
     static bool attr_set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -222,9 +224,11 @@ int max_pair_clusters(int dev) {
     return n;
 }
 
-int launch_pair(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
+int launch_pair(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
                 cudaStream_t stream) {
     using Cfg = TileCfg<256, 32, true>;
+    GemmParams p = params;
+    fill_schedule(p);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * clusters, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -245,8 +249,10 @@ int launch_pair(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& m
 // Convolution kernels: register-staged loader with the implicit im2col gather (MODE 1 forward,
 // 2 weight gradient, 3 input gradient).
 template <int BN, int MODE = 1>
-int launch_conv_cfg(const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_conv_cfg(const GemmParams& params, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN, 32>;
+    GemmParams p = params;
+    fill_schedule(p);
     static bool attr_set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -647,6 +653,7 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         q.total_work = pl.tail_tiles * pl.tail_split;
         rc = launch(q);
         if (rc) return rc;
+        fill_schedule(q);
         tail_reduce_kernel<<<pl.tail_tiles * 8, 256, 0, stream>>>(q, pl.pair ? 2 * kBM : kBM, pl.bn);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         rc = static_cast<int>(cudaGetLastError());
