@@ -1136,7 +1136,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const int n_out = split_out ? 1 : p.n_dest;
                 const bool fuse = !split_out && (p.bias != nullptr || p.addend != nullptr);
                 const bool relu = !split_out && p.relu != 0;
-                const bool plain = n_out == 1 && !fuse && !relu && beta == 0.f && vec;
+                const bool plain = n_out == 1 && !fuse && !relu && beta == 0.f;
                 // compact: element (row, col) of tail tile t lives at
                 //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
@@ -1157,12 +1157,13 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                     __syncwarp();
                     const int col = col_base + g * 32 + chunk * 4;
-                    if (chunk < kChunks && col + 3 < p.N && plain) {
+                    if (chunk < kChunks && col < p.N && plain) {
                         // The common store — one destination (C or the split-K partials), nothing
-                        // fused, whole 16-byte chunks —
-                        // apart from the general one below: a small product is one tile per CTA and
-                        // fetches every instruction it executes cold, so the path it walks is short.
+                        // fused — apart from the general one below: a small product is one tile per
+                        // CTA and fetches every instruction it executes cold, so the path it walks
+                        // is short.
                         float* dst0 = (split_out ? p.partial : p.dest[0]) + base_off + col;
+                        const bool whole = vec && col + 3 < p.N;  // an aligned 16-byte chunk
 #pragma unroll 1
                         for (int it = 0; it < 8; ++it) {
                             const int rr = it * 4 + sub_row;
@@ -1173,7 +1174,15 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                             v.y *= alpha;
                             v.z *= alpha;
                             v.w *= alpha;
-                            *reinterpret_cast<float4*>(dst0 + (long long)row * ld_out) = v;
+                            float* dst = dst0 + (long long)row * ld_out;
+                            if (whole) {
+                                *reinterpret_cast<float4*>(dst) = v;
+                            } else {
+                                dst[0] = v.x;
+                                if (col + 1 < p.N) dst[1] = v.y;
+                                if (col + 2 < p.N) dst[2] = v.z;
+                                if (col + 3 < p.N) dst[3] = v.w;
+                            }
                         }
                     } else if (chunk < kChunks && col < p.N) {
                         // Not unrolled on purpose: 32 copies of the store path (4 column groups x
