@@ -1136,7 +1136,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const int n_out = split_out ? 1 : p.n_dest;
                 const bool fuse = !split_out && (p.bias != nullptr || p.addend != nullptr);
                 const bool relu = !split_out && p.relu != 0;
-                const bool plain = n_out == 1 && !fuse && !relu && beta == 0.f;
+                const bool plain = n_out == 1 && beta == 0.f;
                 // compact: element (row, col) of tail tile t lives at
                 //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
@@ -1158,12 +1158,19 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     __syncwarp();
                     const int col = col_base + g * 32 + chunk * 4;
                     if (chunk < kChunks && col < p.N && plain) {
-                        // The common store — one destination (C or the split-K partials), nothing
-                        // fused — apart from the general one below: a small product is one tile per
+                        // The common store — one destination (C or the split-K partials), no beta —
+                        // apart from the general one below: a small product is one tile per
                         // CTA and fetches every instruction it executes cold, so the path it walks
                         // is short.
                         float* dst0 = (split_out ? p.partial : p.dest[0]) + base_off + col;
                         const bool whole = vec && col + 3 < p.N;  // an aligned 16-byte chunk
+                        float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);  // the same for every row
+                        if (fuse && p.bias != nullptr) {
+                            bias4.x = __ldg(p.bias + col);
+                            if (col + 1 < p.N) bias4.y = __ldg(p.bias + col + 1);
+                            if (col + 2 < p.N) bias4.z = __ldg(p.bias + col + 2);
+                            if (col + 3 < p.N) bias4.w = __ldg(p.bias + col + 3);
+                        }
 #pragma unroll 1
                         for (int it = 0; it < 8; ++it) {
                             const int rr = it * 4 + sub_row;
@@ -1174,6 +1181,27 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                             v.y *= alpha;
                             v.z *= alpha;
                             v.w *= alpha;
+                            if (fuse) {  // bias, then mask, then ReLU: the order of the separate ops
+                                if (p.bias != nullptr) {
+                                    v.x += bias4.x;
+                                    v.y += bias4.y;
+                                    v.z += bias4.z;
+                                    v.w += bias4.w;
+                                }
+                                if (p.addend != nullptr) {
+                                    const float* ad = p.addend + (long long)row * p.ld_addend + col;
+                                    v.x += __ldg(ad);
+                                    if (col + 1 < p.N) v.y += __ldg(ad + 1);
+                                    if (col + 2 < p.N) v.z += __ldg(ad + 2);
+                                    if (col + 3 < p.N) v.w += __ldg(ad + 3);
+                                }
+                            }
+                            if (relu) {
+                                v.x = fmaxf(v.x, 0.f);
+                                v.y = fmaxf(v.y, 0.f);
+                                v.z = fmaxf(v.z, 0.f);
+                                v.w = fmaxf(v.w, 0.f);
+                            }
                             float* dst = dst0 + (long long)row * ld_out;
                             if (whole) {
                                 *reinterpret_cast<float4*>(dst) = v;
