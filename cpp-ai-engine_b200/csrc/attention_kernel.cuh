@@ -76,7 +76,10 @@ __device__ __forceinline__ uint32_t kmajor_offset(int rows, int r, int k) {
 // never read).  Fetching (global loads into registers) and committing (split + shared-memory
 // stores) are separate steps so that the loads of all three operands of a head are in flight
 // together: a head costs one memory round trip, not one per tile.
-constexpr int kAttnFetchBatch = 4;
+#ifndef B200_ATTN_FETCH_BATCH
+#define B200_ATTN_FETCH_BATCH 4
+#endif
+constexpr int kAttnFetchBatch = B200_ATTN_FETCH_BATCH;
 
 struct AttnFetch {
     float4 x[kAttnFetchBatch];
