@@ -338,7 +338,7 @@ def run_b200(args):
             "frac": achieved / sustained,
             # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this workload
             # (profiles/gemm_tf32_kernel_pair_16384cubed_dram.md); algorithmic bytes are 3 * n^2 * 4
-            "traffic": 43067955968 if (n == BIG and kfac == 3) else None,
+            "traffic": 30878857472 if (n == BIG and kfac == 3 and world == 1) else None,
             "algorithmic_bytes": int(3 * n * n * 4),
             "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per product "
                     f"(2*M*N*K*{kfac}) / mean time of one product by CUDA events (at one GPU a product is the "
