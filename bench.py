@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--no-extras", action="store_true", help="skip 4096^3, e2e and the CPU baseline")
     ap.add_argument("--only", default="", help="with --suite engine: run only the shapes whose name contains this text")
+    ap.add_argument("--with-cpu", action="store_true",
+                    help="with --suite engine: also time the reference CPU matmul of each shape on the host cores")
     ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 peak measurement (profiling runs)")
     ap.add_argument("--suite", default="", choices=["", "engine", "accuracy"],
                     help="'engine': time every GEMM of the char-LM, CNN and relu-sparse configurations "
@@ -514,6 +516,36 @@ CONV_SHAPES = [
 ]
 
 
+def cpu_matmul_time(batch, M, N, K, a_batched, b_batched, relu_a=False):
+    """The reference's CPU matmul of one shape on all host threads (the compiled reference engine
+    if it was built, else the C restatement): best of a few runs, bounded to about a second.
+    The transposed forms are timed as the plain product of the same size — the reference
+    materialises the transpose first, so this is a lower bound of what they cost it."""
+    import numpy as np
+
+    from oracle import oracle_py as orc
+
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal(((batch,) if a_batched else ()) + (M, K), dtype=np.float32)
+    if relu_a:  # half of A exactly zero: the reference's loop skips those terms
+        a = np.maximum(a, np.float32(0))
+    b = rng.standard_normal(((batch,) if b_batched else ()) + (K, N), dtype=np.float32)
+    use_ref = orc.have_ref()
+    best, spent, runs = float("inf"), 0.0, 0
+    while runs < 3 or (spent < 0.3 and runs < 50):
+        if use_ref:
+            t = orc.ref_matmul_time(a, b, 1)
+        else:
+            t0 = time.perf_counter()
+            orc.matmul(a, b)
+            t = time.perf_counter() - t0
+        best, spent, runs = min(best, t), spent + t, runs + 1
+        if spent > 1.5:
+            break
+    return {"us": round(best * 1e6, 1), "kind": "reference" if use_ref else "port",
+            "cores": orc.ref_threads() if use_ref else os.cpu_count(), "runs": runs}
+
+
 def run_engine_suite(args):
     import torch
 
@@ -568,13 +600,17 @@ def run_engine_suite(args):
         cold_us = statistics.median(cold)
         bytes_alg = 4.0 * ((batch if ab else 1) * M * K + (batch if bb else 1) * K * N + batch * M * N)
         flops = 2.0 * batch * M * N * K
-        print(json.dumps({
+        record = {
             "shape": name, "batch": batch, "M": M, "N": N, "K": K, "transA": tA, "transB": tB,
             "us_per_launch_back_to_back": round(hot_us, 2), "us_per_launch_l2_flushed": round(cold_us, 2),
             "algorithmic_bytes": int(bytes_alg), "useful_tflops_back_to_back": round(flops / hot_us / 1e6, 3),
             "hbm_gbs_l2_flushed": round(bytes_alg / cold_us / 1e3, 1),
             "frac_of_measured_hbm": round(bytes_alg / cold_us / 1e3 / hbm, 4),
-            "kernels_per_call": 2 if ws_bytes else 1}), flush=True)
+            "kernels_per_call": 2 if ws_bytes else 1}
+        if args.with_cpu:
+            record["cpu"] = cpu_matmul_time(batch, M, N, K, ab, bb, relu_a=("relu" in name or "FF2" in name))
+            record["gpu_over_cpu"] = round(record["cpu"]["us"] / hot_us, 1)
+        print(json.dumps(record), flush=True)
     # the attention core of the char-LM block: 128 heads of 64 x 24, causal mask — one fused kernel
     # against the five separate steps (two products through this library, the rest through torch)
     q, k, v = (torch.randn((32, 4, 64, 24), device=dev, generator=gen) for _ in range(3))
