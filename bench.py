@@ -13,8 +13,15 @@ under "gemm_4096".
 
 One JSON line is printed by rank 0.  `value` is useful TFLOP/s = 2*M*N*K / time (the three
 TF32 products per term and the split are overhead, not counted).  `roofline.achieved` counts
-the tensor-core math actually issued (3 x useful in the default 3xTF32 mode) against the TF32
-tensor-pipe rate measured in the same run with cuBLAS.
+the tensor-core math actually issued per GPU (3 x useful in the default 3xTF32 mode) against a fixed
+peak: TF32 nominal = 1/2 of the pool's measured bf16 rate (MEASURED_PEAKS.json); the cuBLAS TF32
+rate of the same run is carried beside it as context.
+
+Timing: a warm-up of --warmup steps and at least --warm-seconds of back-to-back steps (so that
+every N starts its timed region in the same power state), then windows of exactly --steps steps,
+each between a barrier + synchronize on both sides and timed with CUDA events (max over ranks),
+repeated until a second has been timed; the median window is reported.  Every rank samples its own
+GPU's clocks; `timing.gpu_cycles_per_step_all_gpus` lets scaling be compared clock for clock.
 """
 from __future__ import annotations
 
@@ -48,7 +55,11 @@ def parse_args():
     ap.add_argument("--only", default="", help="with --suite engine: run only the shapes whose name contains this text")
     ap.add_argument("--with-cpu", action="store_true",
                     help="with --suite engine: also time the reference CPU matmul of each shape on the host cores")
-    ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 peak measurement (profiling runs)")
+    ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 context measurement (profiling runs)")
+    ap.add_argument("--warm-seconds", type=float, default=2.0,
+                    help="minimum duration of the untimed warm-up loop (same power state at every N)")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="library option (b200_gemm_set_option), e.g. --opt pdl=0; repeatable")
     ap.add_argument("--suite", default="", choices=["", "engine", "accuracy"],
                     help="'engine': time every GEMM of the char-LM, CNN and relu-sparse configurations "
                          "(one JSON line per shape) instead of the large-square benchmark")
@@ -109,62 +120,97 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
+# shared by both arms
+# ------------------------------------------------------------------------------------------
+def make_config(n: int, world: int, exchange: str, precision: str) -> dict:
+    """The `config` object of the line; the reference arm prints the same one (it times the CPU on
+    the same workload), so that the two arms can be compared key by key."""
+    return {"workload": f"fp32 GEMM {n}^3, A,B ~ N(0,1/K) seed 1, C N-column-sharded over {world} GPU(s), "
+                        f"every rank ends with all of C",
+            "M": n, "N": n, "K": n, "exchange": exchange if world > 1 else "none", "precision": precision,
+            "l2": "operands (1 GiB each) far exceed L2; no flush needed" if n >= 8192
+            else "operands and result together exceed L2; launches back to back"}
+
+
+def measured_peaks() -> dict:
+    """Denominators of the roofline: the pool's measured copy bandwidth and cuBLAS bf16 rates.  TF32
+    is not measured there; the nominal ratio (TF32 dense = 1/2 bf16 dense on this part) is applied to
+    the measured bf16 figures."""
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return {"hbm_gbs": d.get("hbm_gbs", 6650.0), "tf32_burst": 0.5 * d["bf16_tflops"],
+                "tf32_sustained": 0.5 * d["bf16_tflops_sustained"], "kind": "of measured",
+                "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"]}
+    return {"hbm_gbs": 6650.0, "tf32_burst": 0.5 * 1590.0, "tf32_sustained": 0.5 * 1400.0, "kind": "of fallback",
+            "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+# ------------------------------------------------------------------------------------------
 # CPU reference arm
 # ------------------------------------------------------------------------------------------
-def cpu_sample(n: int, rows: int, repeats: int = 1):
-    """Times the reference's CPU matmul on `rows` rows of the n^3 product (rows are independent
-    in its loop, so this is an exact slice of the full job).  Returns (TFLOP/s, info)."""
-    import numpy as np
-
+def cpu_rows(a_rows, b, repeats: int = 1):
+    """The reference's CPU matmul (the unmodified engine when it was built here, else the C
+    restatement) on the given rows of A: rows are independent in its loop, so this is an exact slice
+    of the full product.  Returns (result rows, seconds, info)."""
     from oracle import oracle_py as orc
+
+    if orc.have_ref():
+        kind, cores = "reference", orc.ref_threads()
+        secs = orc.ref_matmul_time(a_rows, b, repeats)
+        out = orc.matmul(a_rows, b)  # the restatement is bit-identical to the engine (tests/test_oracle.py)
+    else:
+        kind, cores = "port", os.cpu_count() or 1
+        best, out = float("inf"), None
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            out = orc.matmul(a_rows, b)
+            best = min(best, time.perf_counter() - t0)
+        secs = best
+    return out, secs, {"kind": kind, "cores": cores}
+
+
+def synthetic_host_inputs(n: int, rows: int):
+    import numpy as np
 
     rng = np.random.default_rng(1)
     scale = 1.0 / np.sqrt(n)
     a = (rng.standard_normal((rows, n), dtype=np.float32) * scale).astype(np.float32)
     b = (rng.standard_normal((n, n), dtype=np.float32) * scale).astype(np.float32)
-    if orc.have_ref():
-        kind, cores = "reference", orc.ref_threads()
-        secs = orc.ref_matmul_time(a, b, repeats)
-    else:
-        kind, cores = "port", os.cpu_count() or 1
-        best = float("inf")
-        for _ in range(repeats):
-            t0 = time.perf_counter()
-            orc.matmul(a, b)
-            best = min(best, time.perf_counter() - t0)
-        secs = best
-    flops = 2.0 * rows * n * n
-    return flops / secs / 1e12, {"kind": kind, "cores": cores, "seconds": secs,
-                                 "sample": f"{rows} of {n} output rows of the {n}^3 product "
-                                           f"(best of {repeats}), all host threads"}
+    return a, b
 
 
 def run_reference(args):
+    """The reference's own CPU implementation of the path on the box's host cores, all threads: each
+    step multiplies a bounded row slice of the workload (rows are independent in its loop) and the
+    line reports whole-product figures extrapolated from it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     n = args.size
     rows = 64 if n >= 8192 else 256
-    tf, info = cpu_sample(n, rows, 1)  # warm-up, also sizes the job
+    a, b = synthetic_host_inputs(n, rows)
+    _, _, info = cpu_rows(a, b)  # warm-up
     for _ in range(max(0, args.warmup - 1)):
-        cpu_sample(n, rows, 1)
-    vals = []
+        cpu_rows(a, b)
+    secs = []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        v, info = cpu_sample(n, rows, 1)
-        vals.append(v)
+        secs.append(cpu_rows(a, b)[1])
         if time.perf_counter() - t0 > 150:
             break
-    value = statistics.mean(vals)
-    ms = 2.0 * rows * n * n / (value * 1e12) * 1e3
+    slice_s = statistics.mean(secs)
+    value = 2.0 * rows * n * n / slice_s / 1e12
+    step_ms = slice_s * (n / rows) * 1e3
+    sample = (f"each step times {rows} of the {n} output rows of the {n}^3 product on all host threads; value and "
+              f"ms_per_step are the whole product's at that rate ({slice_s * 1e3:.1f} ms per slice)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": len(vals), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "steps": len(secs), "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"fp32 GEMM {n}^3, N(0,1/K) inputs; CPU arm times a row slice per step",
-                   "M": n, "N": n, "K": n},
+        "config": make_config(n, args.gpus, args.exchange, args.precision),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
-                         "sample": info["sample"]},
+                         "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -174,9 +220,9 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def measure_tf32_peak(torch, dev, seconds: float = 1.5):
-    """cuBLAS TF32 8192^3: best single launch (burst) and the rate of a back-to-back loop
-    (sustained, what a kernel timed inside a long step should be held against)."""
+def measure_cublas_tf32(torch, dev, seconds: float = 1.5):
+    """cuBLAS TF32 8192^3 in this run, for context (not the roofline's denominator): best single
+    launch (burst) and the rate of a back-to-back loop (sustained)."""
     n = 8192
     old = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = True
@@ -209,7 +255,14 @@ def measure_tf32_peak(torch, dev, seconds: float = 1.5):
     return burst, sustained
 
 
+# sm__pipe_tensor_cycles_active of the 4096^3 main launch (ncu capture summarised under profiles/)
+TENSOR_PIPE_ACTIVE_NCU = {"value": 0.649, "source": "profiles/gemm_tf32_kernel_pair_4096cubed.md"}
+# dram__bytes_read.sum + dram__bytes_write.sum of the launches of one 16384^3 product on one GPU
+DRAM_TRAFFIC_16384 = {"value": 30878857472, "source": "profiles/gemm_tf32_kernel_pair_16384cubed_dram.md"}
+
+
 def run_b200(args):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -217,6 +270,9 @@ def run_b200(args):
 
     pkg = entry.load_package()
     pkg.load()  # raises if the CUDA library is missing: there is no fallback
+    for item in args.opt:
+        name, _, val = item.partition("=")
+        pkg.set_option(name, int(val))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -230,131 +286,192 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
     precision = pkg.PRECISION_3XTF32 if args.precision == "3xtf32" else pkg.PRECISION_TF32
     kfac = 3 if args.precision == "3xtf32" else 1
+    peaks = measured_peaks()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms: float) -> float:
+    def max_over_ranks(x: float) -> float:
         if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    def gather_objects(obj):
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
 
     n = args.size
     gen = torch.Generator(device=dev).manual_seed(1)  # same bytes on every rank
     A = torch.randn((n, n), device=dev, generator=gen) / n ** 0.5
     B = torch.randn((n, n), device=dev, generator=gen) / n ** 0.5
     exchange = args.exchange if world > 1 else "none"
-    try:
-        op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev,
-                                           mode=args.exchange if world > 1 else "nccl")
-    except Exception as exc:  # symmetric memory unavailable: the NCCL gather still works
-        if world > 1 and args.exchange == "fused":
-            if rank == 0:
-                print(f"[bench] fused exchange unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
-            exchange = "nccl"
-            op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev, mode="nccl")
-        else:
-            raise
-    if precision != pkg.PRECISION_3XTF32:
-        def block(A_, B_, dests, col0, cols, _op=op):
-            pkg.gemm_colshard(A_, B_, dests, M=n, N=n, K=n, col0=col0, cols=cols, lda=n, ldb=n, ldc=n,
-                              precision=precision)
-        op._compute = block
-
+    op = None
     if world == 1:
         # one GPU holds every column: the plain entry point with its workspace, which lets the planner
         # split the tiles of a mostly empty last wave along K
+        C = torch.empty((n, n), device=dev)
         ws_bytes = pkg.workspace_bytes(1, n, n, n)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
 
-        def whole(A_, B_, dests, col0, cols, _op=op):
-            pkg.gemm(A_, B_, _op.C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, precision=precision,
+        def step():
+            pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, precision=precision,
                      workspace=ws if ws_bytes else None, workspace_bytes=ws_bytes)
-        op._compute = whole
+    else:
+        try:
+            op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev, mode=args.exchange,
+                                               precision=precision)
+        except Exception as exc:  # symmetric memory unavailable: the NCCL gather still works
+            if args.exchange != "fused":
+                raise
+            if rank == 0:
+                print(f"[bench] fused exchange unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
+            exchange = "nccl"
+            op = pkg.shard.ColumnShardedMatmul(n, n, n, rank=rank, world=world, device=dev, mode="nccl",
+                                               precision=precision)
+        C = op.C
 
-    def step():
-        op(A, B)
+        def step():
+            op(A, B)
 
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed_window(fn, steps):
+        """Exactly `steps` calls between a barrier + synchronize on both sides; CUDA events on the
+        launching stream; max over ranks."""
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # Every rank samples its own GPU's clocks from here to the end of the timed windows.
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()
+    # Warm-up: the requested count (at least 3) AND at least two seconds of back-to-back steps, at
+    # every N, so that every GPU is in the same power state (power-capped, clocks settled) when the
+    # timed windows start — a 0.1 s window on a cold GPU runs at boost clocks a long step never sees.
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
+    t_warm = time.perf_counter()
+    warm_steps = max(3, args.warmup)
+    while True:
+        for _ in range(4):
+            step()
+        warm_steps += 4
+        torch.cuda.synchronize()
+        go_on = 1.0 if time.perf_counter() - t_warm < args.warm_seconds else 0.0
+        if max_over_ranks(go_on) == 0.0:  # every rank leaves the loop in the same round
+            break
     pkg.status()
+    # Timed: windows of exactly --steps steps, repeated until at least one second has been timed;
+    # the line reports the median window.
     launches0 = pkg.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    total_ms = max_over_ranks(e0.elapsed_time(e1))
-    launches = pkg.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    windows = [timed_window(step, args.steps)]
+    while sum(windows) < 1000.0 and len(windows) < 50:
+        windows.append(timed_window(step, args.steps))
+    launches = (pkg.launch_count() - launches0) // len(windows)
+    clocks_mine = sampler.stop()
     pkg.status()
+    total_ms = statistics.median(windows)
     ms = total_ms / args.steps
     flops = 2.0 * n ** 3
     value = flops / ms / 1e9
+    clocks_all = gather_objects(clocks_mine)
+    mhz = [c.get("sm_mhz") for c in clocks_all if c.get("sm_mhz")]
+    slowest_mhz = min(mhz) if mhz else None
 
-    # parity spot check of the timed result: sampled rows against fp64 on the device
+    # ------------------------------------------------------------------ parity of the timed result
+    # Every rank checks sampled rows of ITS copy of C, all columns (so the peers' stores are covered),
+    # against fp64 on the device; two checksums of the whole of C are compared across ranks.
     rows = torch.arange(3, n, max(1, n // 16), device=dev)
     ref = A[rows].double() @ B.double()
-    err = float(((op.C[rows].double() - ref).abs() / ref.abs().clamp(min=1.0)).max().item())
+    err = float(((C[rows].double() - ref).abs() / ref.abs().clamp(min=1.0)).max().item())
     del ref
+    err_all = max_over_ranks(err)
+    sums = (int(C.view(torch.int32).sum(dtype=torch.int64).item()),
+            int(C.view(torch.int32)[:, ::3].sum(dtype=torch.int64).item()))
+    same_everywhere = len(set(gather_objects(sums))) == 1
+
+    # ------------------------------------------------------------------ what the exchange costs (N > 1)
+    breakdown = None
+    if world > 1 and exchange == "fused" and not args.no_extras:
+        own, peer_c = op.C, [op._peer_views[0][(rank + i) % world] for i in range(world)]
+
+        def local_only():
+            pkg.gemm_colshard(A, B, [own], M=n, N=n, K=n, col0=op.col0, cols=op.cols, lda=n, ldb=n, ldc=n,
+                              precision=precision)
+
+        def with_stores():
+            pkg.gemm_colshard(A, B, peer_c, M=n, N=n, K=n, col0=op.col0, cols=op.cols, lda=n, ldb=n, ldc=n,
+                              precision=precision)
+
+        k = max(4, args.steps)
+        t_local = timed_window(local_only, k) / k
+        t_stores = timed_window(with_stores, k) / k
+        t_full = timed_window(step, k) / k
+        breakdown = {"own_columns_only_ms": t_local, "with_peer_stores_ms": t_stores, "with_barriers_ms": t_full,
+                     "peer_stores_cost_ms": t_stores - t_local, "barriers_cost_ms": t_full - t_stores,
+                     "nvlink_bytes_stored_per_rank": int(n * op.cols * 4 * (world - 1)),
+                     "note": "product kernel on this rank's columns with no peer destination / with the forwarder "
+                             "warps storing every tile into the peers / the whole call with its two barriers; "
+                             "each timed like the main windows (max over ranks)"}
 
     line = None
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "warmup": warm_steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)"
             if kfac == 3 else "tf32", "data": "synthetic",
-            "config": {"workload": f"fp32 GEMM {n}^3, A,B ~ N(0,1/K) seed 1, C N-column-sharded over "
-                                   f"{world} GPU(s), every rank ends with all of C",
-                       "M": n, "N": n, "K": n, "exchange": exchange, "precision": args.precision,
-                       "l2": "operands (1 GiB each) far exceed L2; no flush needed"
-                       if n >= 8192 else "L2 flushed between timed launches"},
-            "gpu_launches": int(launches), "clocks": clocks,
-            "check": {"scaled_max_error_vs_fp64_sampled_rows": err},
+            "config": make_config(n, world, exchange, args.precision),
+            "gpu_launches": int(launches),
+            "timing": {"windows_ms": [round(w, 3) for w in windows], "reported": "median window / steps",
+                       "warmup_seconds": round(time.perf_counter() - t_warm, 2),
+                       "cycles_per_step_slowest_gpu": ms * 1e3 * slowest_mhz if slowest_mhz else None,
+                       "gpu_cycles_per_step_all_gpus": ms * 1e3 * slowest_mhz * world if slowest_mhz else None,
+                       "note": "cycles = ms x median SM MHz under load of the slowest-clocked rank; "
+                               "clock-normalised scaling efficiency = gpu_cycles_per_step_all_gpus at N=1 / at N"},
+            "clocks": {"sm_mhz": slowest_mhz, "sm_max_mhz": clocks_all[0].get("sm_max_mhz"),
+                       "reasons": sorted({r for c in clocks_all for r in c.get("reasons", [])}),
+                       "sm_mhz_per_rank": [c.get("sm_mhz") for c in clocks_all],
+                       "power_w_max_per_rank": [c.get("power_w_max") for c in clocks_all]},
+            "check": {"scaled_max_error_vs_fp64_sampled_rows_max_over_ranks": err_all,
+                      "all_ranks_hold_the_same_c": same_everywhere},
+        }
+        if breakdown:
+            line["exchange_breakdown"] = breakdown
+        achieved = kfac * value / world  # tensor-core TF32 math per GPU
+        line["roofline"] = {
+            "bound": "tensor", "achieved": achieved, "peak": peaks["tf32_sustained"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["tf32_sustained"],
+            "traffic": DRAM_TRAFFIC_16384["value"] if (n == BIG and kfac == 3 and world == 1) else None,
+            "traffic_source": DRAM_TRAFFIC_16384["source"] if (n == BIG and kfac == 3 and world == 1) else None,
+            "algorithmic_bytes": int(3 * n * n * 4),
+            "peak_kind": f"TF32 nominal = 1/2 measured bf16 (sustained, {peaks['bf16_tflops_sustained']} TFLOP/s; "
+                         f"{peaks['kind']}): this step runs inside a long power-capped loop",
+            "note": f"achieved = {kfac} x useful TFLOP/s per GPU: the TF32 tensor-core math issued per product "
+                    f"(2*M*N*K*{kfac}) / mean time of one product by CUDA events; at one GPU a product is the main "
+                    f"launch plus the K-split launch of the last wave's tiles and their reduction",
+            "useful_tflops_per_gpu": value / world, "useful_frac": value / world / peaks["tf32_sustained"],
+            "k_factor": kfac, "tensor_pipe_active_ncu": TENSOR_PIPE_ACTIVE_NCU,
         }
 
     extras = (world == 1 and not args.no_extras)
-    # ------------------------------------------------------------------ roofline (rank 0, N = 1)
-    if rank == 0 and world == 1:
-        if args.no_peak:
-            burst = sustained = float("nan")
-        else:
-            time.sleep(2.0)  # let the power-capped clocks recover before the burst measurement
-            burst, sustained = measure_tf32_peak(torch, dev)
-        peaks_file = ROOT / "MEASURED_PEAKS.json"
-        bf16 = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
-        achieved = kfac * value
-        line["roofline"] = {
-            "bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s",
-            "frac": achieved / sustained,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this workload
-            # (profiles/gemm_tf32_kernel_pair_16384cubed_dram.md); algorithmic bytes are 3 * n^2 * 4
-            "traffic": 30878857472 if (n == BIG and kfac == 3 and world == 1) else None,
-            "algorithmic_bytes": int(3 * n * n * 4),
-            "note": f"achieved = {kfac} x useful TFLOP/s: tensor-core TF32 math issued per product "
-                    f"(2*M*N*K*{kfac}) / mean time of one product by CUDA events (at one GPU a product is the "
-                    f"main launch plus the K-split launch of the last wave's tiles and their reduction; "
-                    f"traffic is the ncu figure of the single-launch plan); peak = cuBLAS TF32 8192^3 "
-                    f"sustained loop measured in this run (of measured); burst {burst:.1f}",
-            "useful_tflops": value, "useful_frac": value / sustained, "k_factor": kfac,
-            "peak_burst": burst,
-            "bf16_measured_peaks": {k: bf16.get(k) for k in ("bf16_tflops", "bf16_tflops_sustained")},
-        }
-    if world > 1 and rank == 0:
-        line["roofline"] = {"bound": "tensor", "achieved": kfac * value, "peak": None, "unit": "TFLOP/s",
-                            "frac": None, "traffic": None,
-                            "note": "whole-job tensor math over all ranks; see the N=1 line for the per-GPU peak"}
+    if extras and not args.no_peak:
+        time.sleep(2.0)  # let the power-capped clocks recover before the burst measurement
+        burst, sustained = measure_cublas_tf32(torch, dev)
+        line["roofline"]["cublas_tf32_same_run"] = {"burst": burst, "sustained": sustained,
+                                                    "vs_cublas_tf32_sustained": kfac * value / sustained}
 
     # ------------------------------------------------------------------ 4096^3 (N = 1)
     if extras:
@@ -363,7 +480,6 @@ def run_b200(args):
         b4 = torch.randn((m, m), device=dev, generator=gen) / m ** 0.5
         c4 = torch.empty((m, m), device=dev)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
         ws4_bytes = pkg.workspace_bytes(1, m, m, m)  # the tail-wave plan needs scratch for its partials
         ws4 = torch.empty(max(ws4_bytes, 16), dtype=torch.uint8, device=dev)
 
@@ -371,11 +487,10 @@ def run_b200(args):
             pkg.gemm(a4, b4, c4, batch=1, M=m, N=m, K=m, lda=m, ldb=m, ldc=m, precision=precision,
                      workspace=ws4, workspace_bytes=ws4_bytes)
 
-        time.sleep(2.0)  # same starting state as the burst peak it is compared with
+        time.sleep(2.0)  # the state a burst peak is measured in: idle for two seconds
         for _ in range(3):
             launch4()
         torch.cuda.synchronize()
-        # (a) back to back: A, B and C together (201 MB) exceed the 126 MB L2
         iters = max(20, args.steps)
         e0.record()
         for _ in range(iters):
@@ -383,7 +498,6 @@ def run_b200(args):
         e1.record()
         torch.cuda.synchronize()
         b2b_ms = e0.elapsed_time(e1) / iters
-        # (b) one launch per timing with L2 evicted before each
         times = []
         for _ in range(iters):
             flush.fill_(1)
@@ -395,82 +509,106 @@ def run_b200(args):
         pkg.status()
         cold_ms = statistics.mean(times)
         tf = 2.0 * m ** 3 / b2b_ms / 1e9
-        peak4 = line["roofline"]["peak_burst"]
         line["gemm_4096"] = {
             "workload": "fp32 GEMM 4096^3, N(0,1/K); back-to-back launches (A+B+C = 201 MB exceed L2)",
             "ms_per_launch": b2b_ms, "useful_tflops": tf, "tensor_math_tflops": kfac * tf,
-            "frac_of_tf32_peak": kfac * tf / peak4, "peak": peak4,
-            "peak_kind": "cuBLAS TF32 8192^3 burst (best single launch after 2 s idle) measured in this run; "
-                         "this product is timed the same way: a 20-launch burst after 2 s idle",
+            "frac_of_tf32_peak": kfac * tf / peaks["tf32_burst"], "peak": peaks["tf32_burst"],
+            "peak_kind": f"TF32 nominal = 1/2 measured bf16 (burst, {peaks['bf16_tflops']} TFLOP/s; {peaks['kind']}); "
+                         f"this product is timed as a burst too: 20 launches after 2 s idle",
+            "tensor_pipe_active_ncu": TENSOR_PIPE_ACTIVE_NCU,
             "l2_flushed": {"ms_mean": cold_ms, "ms_best": min(times),
                            "useful_tflops": 2.0 * m ** 3 / cold_ms / 1e9,
                            "note": "single launch after a 256 MB fill that evicts L2"},
         }
         del a4, b4, c4, flush
 
+    # ------------------------------------------------------------------ engine-sized products (N = 1)
+    if extras:
+        line["engine"] = engine_block(pkg, torch, dev, peaks["hbm_gbs"])
+
     # ------------------------------------------------------------------ end to end, host buffers
-    if world == 1 and not args.no_extras:
-        import numpy as np
-
-        h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
-        h_b = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
-        h_c = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
-        h_a.copy_(A)
-        h_b.copy_(B)
-        del op
-        torch.cuda.empty_cache()
-        na, nb, nc = h_a.numpy(), h_b.numpy(), h_c.numpy()
+    e2e = None
+    if not args.no_extras:
         reps = max(2, min(args.steps, 4))
-        pkg.matmul_host(na, nb, nc, batch=1, rows=n, inner=n, cols=n, a_batched=False, b_batched=False)
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            pkg.matmul_host(na, nb, nc, batch=1, rows=n, inner=n, cols=n, a_batched=False, b_batched=False)
-        secs = (time.perf_counter() - t0) / reps
-        line["e2e"] = {"value": flops / secs / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(2 * n * n * 4),
-                       "d2h_bytes_per_step": int(n * n * 4), "ms_per_step": secs * 1e3,
-                       "path": "b200_matmul_f32_host: pinned host A,B -> device, kernel, C -> pinned host, synchronised"}
-        assert np.isfinite(nc[::997, ::991]).all()
-    elif world > 1:
-        # every rank uploads A and its B columns from pinned memory and downloads its C columns
-        col0, cols = op.col0, op.cols
-        h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
-        h_b = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)
-        h_c = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)
-        h_a.copy_(A)
-        if cols:
+        if world == 1:
+            h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+            h_b = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+            h_c = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+            h_a.copy_(A)
+            h_b.copy_(B)
+            keep_rows = A[:64].cpu().numpy()  # for the CPU leg below
+            b_host = h_b.numpy()
+            del C
+            torch.cuda.empty_cache()
+            na, nb, nc = h_a.numpy(), h_b.numpy(), h_c.numpy()
+
+            def e2e_step():
+                pkg.matmul_host(na, nb, nc, batch=1, rows=n, inner=n, cols=n, a_batched=False, b_batched=False)
+
+            path = "b200_matmul_f32_host: pinned host A, B -> device, kernels, C -> pinned host, synchronised"
+            h2d, d2h = int(2 * n * n * 4), int(n * n * 4)
+        else:
+            hop = pkg.shard.ShardedHostMatmul(n, n, n, rank=rank, world=world, device=dev)
+            per, cols, col0 = hop.rows_per_rank, hop.cols, hop.col0
+            h_a = torch.empty((per, n), dtype=torch.float32, pin_memory=True)
+            h_b = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)[:, :cols]
+            h_c = torch.empty((n, max(cols, 1)), dtype=torch.float32, pin_memory=True)[:, :cols]
+            h_a.copy_(A[rank * per:(rank + 1) * per])
             h_b.copy_(B[:, col0:col0 + cols])
-        reps = max(2, min(args.steps, 4))
+            na, nb, nc = h_a.numpy(), h_b.numpy(), h_c.numpy()
 
-        def e2e_step():
-            A.copy_(h_a, non_blocking=True)
-            if cols:
-                B[:, col0:col0 + cols].copy_(h_b, non_blocking=True)
-            op(A, B)
-            if cols:
-                h_c.copy_(op.C[:, col0:col0 + cols], non_blocking=True)
-            torch.cuda.synchronize()
+            def e2e_step():
+                hop(na, nb, nc)
 
+            path = ("b200_matmul_f32_host_sharded: every rank uploads 1/N of A's rows and its own columns of B "
+                    "from pinned memory, the rows are all-gathered over NVLink chunk by chunk, strips are "
+                    "multiplied as they arrive, the own columns of C return to pinned memory; bytes are the "
+                    "whole job's (sum over ranks)")
+            h2d, d2h = int(2 * n * n * 4), int(n * n * 4)
         e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(reps):
             e2e_step()
+        torch.cuda.synchronize()
+        secs = max_over_ranks((time.perf_counter() - t0) / reps)
         barrier()
-        secs = max_over_ranks((time.perf_counter() - t0) / reps * 1e3) / 1e3
-        if rank == 0:
-            line["e2e"] = {"value": flops / secs / 1e12, "unit": "TFLOP/s",
-                           "h2d_bytes_per_step": int((n * n + n * cols) * 4), "d2h_bytes_per_step": int(n * cols * 4),
-                           "ms_per_step": secs * 1e3,
-                           "path": "per rank: pinned host A + B columns -> device, sharded kernel + exchange, "
-                                   "own C columns -> pinned host; bytes are per rank"}
-    elif rank == 0:
-        line["e2e"] = None
+        pkg.status()
+        # the result that came back, against fp64 of the same inputs (sampled rows, own columns)
+        rr = torch.arange(5, n, max(1, n // 8), device=dev)
+        if world == 1:
+            got = torch.from_numpy(nc[rr.cpu().numpy()]).to(dev)
+            ref = A[rr].double() @ B.double()
+        else:
+            got = torch.from_numpy(np.ascontiguousarray(nc[rr.cpu().numpy()])).to(dev)
+            ref = A[rr].double() @ B[:, col0:col0 + cols].double()
+        e2e_err = max_over_ranks(float(((got.double() - ref).abs() / ref.abs().clamp(min=1.0)).max().item())
+                                 if got.numel() else 0.0)
+        e2e = {"value": flops / secs / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": secs * 1e3, "path": path,
+               "scaled_max_error_vs_fp64_sampled_rows": e2e_err}
+    if rank == 0:
+        line["e2e"] = e2e
 
-    # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1)
+    # ------------------------------------------------------------------ CPU baseline + parity (rank 0, N = 1)
     if rank == 0 and world == 1 and not args.no_extras:
-        tf, info = cpu_sample(n, 64, 1)
+        # the reference's CPU matmul on the first 64 rows of the SAME A and B: timed (the baseline) and,
+        # as the checker, compared with the rows the device path returned and with fp64
+        cpu_out, cpu_s, info = cpu_rows(keep_rows, b_host)
+        tf = 2.0 * 64 * n * n / cpu_s / 1e12
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
-                                "sample": info["sample"]}
+                                "sample": f"64 of {n} output rows of this {n}^3 product (rows are independent in "
+                                          f"the reference loop), all host threads, {cpu_s * 1e3:.0f} ms"}
+        ref64 = keep_rows.astype(np.float64) @ b_host.astype(np.float64)
+        gpu_rows = nc[:64]
+
+        def scaled(x, y):
+            return float(np.max(np.abs(x - y) / np.maximum(1.0, np.abs(y))))
+
+        line["parity"] = {"rows": 64, "gpu_vs_cpu_loop": scaled(gpu_rows, cpu_out), "gpu_vs_fp64": scaled(gpu_rows, ref64),
+                          "cpu_loop_vs_fp64": scaled(cpu_out, ref64), "bar_vs_cpu_loop": 1e-5,
+                          "note": "scaled max error |x - y| / max(1, |y|) on the first 64 rows of the product that "
+                                  "the end-to-end call returned"}
     elif rank == 0:
         line["cpu_baseline"] = None
 
@@ -546,6 +684,91 @@ def cpu_matmul_time(batch, M, N, K, a_batched, b_batched, relu_a=False):
             "cores": orc.ref_threads() if use_ref else os.cpu_count(), "runs": runs}
 
 
+# the engine-sized products the default line carries (configurations 1-3): name, batch, M, N, K, tA, tB, ab, bb
+ENGINE_BLOCK_SHAPES = [
+    ("cfg1 512^3", 1, 512, 512, 512, 0, 0, 0, 0),
+    ("cfg2 FF1 fwd 2048x96x384", 1, 2048, 384, 96, 0, 0, 0, 0),
+    ("cfg2 dW=X^T.dY 96x2048x384 TN (split-K)", 1, 96, 384, 2048, 1, 0, 0, 0),
+    ("cfg2 scores Q.K^T 128x[64x24x64] NT", 128, 64, 64, 24, 0, 1, 1, 1),
+    ("cfg3 conv1 im2col 50176x9x8 NT", 1, 50176, 8, 9, 0, 1, 0, 0),
+]
+
+
+def engine_block(pkg, torch, dev, hbm_gbs):
+    """Per-launch figures of the engine-sized products and of the two convolution layers as single
+    implicit-GEMM kernels: microseconds back to back and after an L2 flush, the fraction of the
+    measured HBM bandwidth their algorithmic bytes reach, and the reference's CPU matmul of the same
+    shape on the host cores beside it."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    out = []
+
+    def time_call(launch):
+        for _ in range(5):
+            launch()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(50):
+            launch()
+        e1.record()
+        torch.cuda.synchronize()
+        hot = e0.elapsed_time(e1) / 50 * 1e3
+        cold = []
+        for _ in range(10):
+            flush.fill_(1)
+            e0.record()
+            launch()
+            e1.record()
+            torch.cuda.synchronize()
+            cold.append(e0.elapsed_time(e1) * 1e3)
+        pkg.status()
+        return hot, statistics.median(cold)
+
+    for name, batch, M, N, K, tA, tB, ab, bb in ENGINE_BLOCK_SHAPES:
+        a_shape = ((batch,) if ab else ()) + ((K, M) if tA else (M, K))
+        b_shape = ((batch,) if bb else ()) + ((N, K) if tB else (K, N))
+        A = torch.randn(a_shape, device=dev, generator=gen)
+        B = torch.randn(b_shape, device=dev, generator=gen)
+        C = torch.empty((batch, M, N), device=dev)
+        ws_bytes = pkg.workspace_bytes(batch, M, N, K)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+        def launch():
+            pkg.gemm(A, B, C, batch=batch, M=M, N=N, K=K, transA=bool(tA), transB=bool(tB),
+                     lda=a_shape[-1], ldb=b_shape[-1], ldc=N, strideA=(K * M if ab else 0),
+                     strideB=(K * N if bb else 0), strideC=M * N, workspace=ws, workspace_bytes=ws_bytes)
+
+        hot, cold = time_call(launch)
+        bytes_alg = 4.0 * ((batch if ab else 1) * M * K + (batch if bb else 1) * K * N + batch * M * N)
+        cpu = cpu_matmul_time(batch, M, N, K, ab, bb)
+        out.append({"shape": name, "us_back_to_back": round(hot, 2), "us_l2_flushed": round(cold, 2),
+                    "algorithmic_bytes": int(bytes_alg),
+                    "frac_of_measured_hbm": round(bytes_alg / cold / 1e3 / hbm_gbs, 4),
+                    "kernels_per_call": pkg.plan(batch, M, N, K, ws_bytes)["kernels"],
+                    "cpu_reference_us": cpu["us"], "cpu_kind": cpu["kind"], "cpu_cores": cpu["cores"]})
+    for name, n, c, h, w, out_c, k, stride, pad in CONV_SHAPES:
+        x = torch.rand((n, c, h, w), device=dev, generator=gen)
+        wt = torch.randn((out_c, c, k, k), device=dev, generator=gen)
+        b = torch.randn((out_c,), device=dev, generator=gen)
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        y = torch.empty((n, out_c, oh, ow), device=dev)
+
+        def launch():
+            pkg.lib.conv2d_forward(x, wt, b, y, n=n, c=c, h=h, w=w, out_c=out_c, kh=k, kw=k, stride=stride, pad=pad)
+
+        hot, cold = time_call(launch)
+        bytes_alg = 4.0 * (x.numel() + wt.numel() + b.numel() + y.numel())
+        cpu = cpu_matmul_time(1, n * oh * ow, out_c, c * k * k, 0, 0)
+        out.append({"shape": name, "us_back_to_back": round(hot, 2), "us_l2_flushed": round(cold, 2),
+                    "algorithmic_bytes": int(bytes_alg),
+                    "frac_of_measured_hbm": round(bytes_alg / cold / 1e3 / hbm_gbs, 4), "kernels_per_call": 1,
+                    "cpu_reference_us": cpu["us"], "cpu_kind": cpu["kind"], "cpu_cores": cpu["cores"],
+                    "cpu_note": "the reference's CPU matmul of the layer's im2col product alone (its im2col, bias "
+                                "and permute passes are not counted)"})
+    return out
+
+
 def run_engine_suite(args):
     import torch
 
@@ -606,7 +829,7 @@ def run_engine_suite(args):
             "algorithmic_bytes": int(bytes_alg), "useful_tflops_back_to_back": round(flops / hot_us / 1e6, 3),
             "hbm_gbs_l2_flushed": round(bytes_alg / cold_us / 1e3, 1),
             "frac_of_measured_hbm": round(bytes_alg / cold_us / 1e3 / hbm, 4),
-            "kernels_per_call": 2 if ws_bytes else 1}
+            "kernels_per_call": pkg.plan(batch, M, N, K, ws_bytes)["kernels"]}
         if args.with_cpu:
             record["cpu"] = cpu_matmul_time(batch, M, N, K, ab, bb, relu_a=("relu" in name or "FF2" in name))
             record["gpu_over_cpu"] = round(record["cpu"]["us"] / hot_us, 1)

@@ -21,11 +21,20 @@ from .lib import (  # noqa: F401
     gemm,
     gemm_colshard,
     gemm_fused,
+    gemm_sharded,
+    matmul_host_sharded,
+    ShardComm,
+    SHARD_FUSED,
+    SHARD_NCCL,
+    shard_columns,
+    shard_host_plan,
     gemm_static_scratch,
     launch_count,
     lib_path,
     load,
     matmul_host,
+    plan,
+    selftest_timeout,
     set_option,
     status,
     workspace_bytes,

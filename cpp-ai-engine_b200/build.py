@@ -9,14 +9,15 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libb200gemm.so"
-SOURCES = [CSRC / "gemm_sm100.cu"]
-HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "attention_kernel.cuh", CSRC / "attention_bwd_kernel.cuh", CSRC / "sm100_ptx.cuh", PKG_DIR.parent / "include" / "b200_gemm.h"]
+SOURCES = [CSRC / "gemm_sm100.cu", CSRC / "shard_sm100.cu"]
+HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "attention_kernel.cuh", CSRC / "attention_bwd_kernel.cuh", CSRC / "sm100_ptx.cuh", CSRC / "shard_layout.h", PKG_DIR.parent / "include" / "b200_gemm.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",
     "-cudart", "static",
+    "-ldl",  # NCCL is resolved at run time (dlopen), never linked
 ]
 
 
@@ -93,4 +94,24 @@ def build_host_tests(force: bool = False) -> Path:
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("host test build failed:\n" + proc.stdout + proc.stderr)
+    return exe
+
+
+def build_shard_test(force: bool = False) -> Path:
+    """Compiles tests/cpp/test_shard_b200 (a C++ caller of the sharded product on two GPUs; links the
+    CUDA library and, as its checker, the oracle; NCCL is found at run time)."""
+    root = PKG_DIR.parent
+    src = root / "tests" / "cpp" / "test_shard_b200.cpp"
+    exe = root / "tests" / "cpp" / "test_shard_b200"
+    build_library()
+    if not force and exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, LIB.stat().st_mtime):
+        return exe
+    cmd = [cxx_path(), "-std=c++17", "-O2", "-Wall", "-Wextra", str(src), "-I", str(root / "include"),
+           "-I", str(CUDA_HOME / "include"), "-o", str(exe), "-L", str(PKG_DIR), "-lb200gemm",
+           "-L", str(root / "oracle"), "-loracle", "-L", str(CUDA_HOME / "lib64"), "-lcudart", "-ldl",
+           "-Wl,-rpath,$ORIGIN/../../cpp-ai-engine_b200", "-Wl,-rpath,$ORIGIN/../../oracle",
+           f"-Wl,-rpath,{CUDA_HOME / 'lib64'}", "-lpthread"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("shard test build failed:\n" + proc.stdout + proc.stderr)
     return exe

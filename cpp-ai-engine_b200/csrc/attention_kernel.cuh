@@ -50,16 +50,7 @@ struct AttnParams {
     float scale;
     int precision;
     int* status;
-#ifdef B200_ATTN_PROFILE
-    long long* prof;  // development builds: per-phase clock64 stamps of CTA 0
-#endif
 };
-
-#ifdef B200_ATTN_PROFILE
-#define ATTN_STAMP(i) do { if (p.prof && blockIdx.x == 0 && threadIdx.x == 32) p.prof[i] = clock64(); } while (0)
-#else
-#define ATTN_STAMP(i) do { } while (0)
-#endif
 
 // Byte offset of element (row r, k) in a K-major, 128-byte-swizzled tile made of k-blocks of 32
 // floats; k-block kb of a tile with `rows` rows starts at kb * rows * 128.
@@ -228,7 +219,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
     volatile int* abort_flag = &abort_s;
     const bool mask_vec = p.mask != nullptr && (p.s_k & 3) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 15u) == 0;
-    ATTN_STAMP(0);
 
     uint32_t phase = 0;
     for (int b = blockIdx.x; b < p.batch; b += gridDim.x, phase ^= 1) {
@@ -254,7 +244,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
             fence_proxy_async_smem();
         }
         __syncthreads();
-        ATTN_STAMP(1);
         // ---- 2. S = Q x K^T
         if (threadIdx.x == 0) {
             tc_fence_after_sync();
@@ -291,7 +280,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
                 *abort_flag = 1;
             }
             tc_fence_after_sync();
-            ATTN_STAMP(2);
             const uint32_t t0 = tmem_s + (static_cast<uint32_t>((warp & 3) * 32) << 16) + col0;
             float max_v = -INFINITY;
             if (ok && warp_has_rows) {
@@ -384,7 +372,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
             fence_proxy_async_smem();
         }
         __syncthreads();
-        ATTN_STAMP(3);
         if (*abort_flag) break;
         // ---- 4. O = P x V
         if (threadIdx.x == 0) {
@@ -402,7 +389,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
                 *abort_flag = 1;
             } else if (warp_has_rows) {
                 tc_fence_after_sync();
-                ATTN_STAMP(4);
                 const uint32_t t0 = tmem_o + (static_cast<uint32_t>((warp & 3) * 32) << 16);
                 float* obase = p.out + bb * p.o_bs + bh * p.o_hs;
                 const bool ovec = (p.o_ld & 3) == 0 && (reinterpret_cast<uintptr_t>(obase) & 15u) == 0;
@@ -433,7 +419,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_fwd_kernel(const At
             tc_fence_before_sync();
         }
         __syncthreads();  // shared memory and TMEM are reused by the next head
-        ATTN_STAMP(5);
         if (*abort_flag) break;
     }
 

@@ -60,6 +60,8 @@ constexpr int kStatProducer = 1;
 constexpr int kStatMma = 2;
 constexpr int kStatWorkerFull = 4;
 constexpr int kStatWorkerAcc = 8;
+constexpr int kStatForwarder = 16;
+constexpr int kStatSelfTest = 32;
 
 struct GemmParams {
     int M, N, K, batch;
@@ -77,6 +79,7 @@ struct GemmParams {
     unsigned long long fd_split, fd_tiles, fd_band, fd_rows, fd_rows_last;
     int promote_every;  // k-blocks per TMEM accumulation chain
     int tf32_round;     // TF32 mode with the TMA loader: 1 = workers round the tile to nearest first
+    int trunc_hi;       // 3xTF32 with the TMA loader: 1 = the head is the tensor core's own truncation
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
     // fused epilogue: out = act(alpha*acc + beta*out + bias[col] + addend[row][col])
     const float* bias;    // N values, or null
@@ -99,9 +102,6 @@ struct GemmParams {
     uint32_t idesc;
     // loader / epilogue fast paths
     int a_vec_ok, b_vec_ok, c_vec_ok;
-#ifdef B200_PHASE_PROFILE
-    unsigned long long* prof;  // development only: cycles per phase, CTA 0
-#endif
 };
 
 template <int BN, int BK, bool kPair = false>
@@ -172,7 +172,7 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int w) {
 // kCluster: the barrier is also arrived on by the peer CTA, whose writes must be acquired.
 template <bool kCluster = false>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                         int* status, int code) {
+                                         int* status, int code, uint64_t budget_ns = kWaitBudgetNs) {
     auto probe = [&]() { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
     if (probe()) return true;
     const uint64_t start = global_timer_ns();
@@ -182,29 +182,13 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
             if (probe()) return true;
         }
         if (*abort_flag) return false;
-        if (global_timer_ns() - start > kWaitBudgetNs) {
+        if (global_timer_ns() - start > budget_ns) {
             atomicOr(status, code);
             *abort_flag = 1;
             return false;
         }
     }
 }
-
-#ifdef B200_PHASE_PROFILE
-#define B200_T0() const long long _t0 = clock64()
-#define B200_T1(idx) _prof[idx] += clock64() - _t0
-#define B200_PROF_DECL long long _prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define B200_PROF_FLUSH(cond)                                                        \
-    if ((cond) && blockIdx.x == 0 && p.prof) {                                       \
-        for (int _i = 0; _i < 12; ++_i)                                              \
-            if (_prof[_i]) atomicAdd(p.prof + _i, (unsigned long long)_prof[_i]);    \
-    }
-#else
-#define B200_T0()
-#define B200_T1(idx)
-#define B200_PROF_DECL
-#define B200_PROF_FLUSH(cond)
-#endif
 
 // The fused part of the epilogue, in the order the reference applies its separate operations
 // to a product: bias broadcast add (src/nn.cpp:120-122, src/conv.cpp:323), additive mask
@@ -641,6 +625,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     __shared__ __align__(8) uint64_t acce_bar[2];         // accumulator drained
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
+    __shared__ uint32_t fwd_count_s;  // worker warps that have stored their part of a tile (column-shard gather)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -661,6 +646,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             mbar_init(smem_u32(&acce_bar[b]), kArrivals);
         }
         abort_s = 0;
+        fwd_count_s = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -686,6 +672,10 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     }
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
+    // Everything above (barriers, tensor memory, descriptor prefetch) touched no global data and may
+    // have run while the previous kernel of the stream was still finishing; from here on this
+    // kernel reads and writes memory that kernel may own.
+    grid_dependency_wait();
     const bool prec3 = (p.precision == 0);
     const int promote_every = p.promote_every;
 
@@ -698,7 +688,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         if (kTma && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            B200_PROF_DECL;
             for (int w = first_work; w < p.total_work && ok; w += work_stride) {
                 const Work wk = decode_work(p, w);
                 const int za = p.strideA ? wk.b : 0;
@@ -707,10 +696,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     {
-                        B200_T0();
                         const bool got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag,
                                                   p.status, kStatProducer);
-                        B200_T1(0);
                         if (!got) {
                             ok = false;
                             break;
@@ -738,7 +725,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
-            B200_PROF_FLUSH(true);
             if (!ok) {
                 // Leave no bulk copy in flight behind an exiting CTA: give the loads already
                 // issued a short while to land.
@@ -775,7 +761,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             };
             uint32_t it = 0, chain = 0;
             bool ok = true;
-            B200_PROF_DECL;
             for (int w = first_work; w < p.total_work && ok; w += work_stride) {
                 const Work wk = decode_work(p, w);
                 const int nkb = wk.kb1 - wk.kb0;
@@ -786,21 +771,17 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     const bool chain_end = ((i + 1) % promote_every) == 0 || i == nkb - 1;
                     const uint32_t buf = chain & 1;
                     if (chain_start) {
-                        B200_T0();
                         const bool got = wait_bar<kPair>(smem_u32(&acce_bar[buf]),
                                                          ((chain >> 1) & 1) ^ 1, abort_flag,
                                                          p.status, kStatMma);
-                        B200_T1(2);
                         if (!got) {
                             ok = false;
                             break;
                         }
                     }
                     {
-                        B200_T0();
                         const bool got = wait_bar<kPair>(smem_u32(&split_bar[s]), ph, abort_flag,
                                                          p.status, kStatMma);
-                        B200_T1(3);
                         if (!got) {
                             ok = false;
                             break;
@@ -838,7 +819,79 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
-            B200_PROF_FLUSH(true);
+        }
+      } else if constexpr (kConv == 0) {
+        // ------------------------------------------------------------------ forwarders (warps 2, 3)
+        // Column-shard gather: the workers store a finished tile into this GPU's own C and go
+        // straight back to splitting; these two otherwise idle warps then copy the tile from
+        // there (it is still in L2) into every peer's C with plain stores over NVLink.  A store
+        // to a peer is posted, but an SM can only keep so many in flight: issued by the workers,
+        // seven remote copies per tile stalled the whole pipeline once per tile.  The source is
+        // global memory that nobody overwrites during the launch, so the forwarders may fall
+        // any number of tiles behind; they catch up under the next tiles' math.
+        if (p.n_dest > 1) {
+            const int ftid = static_cast<int>(threadIdx.x) - 64;
+            const uint32_t cnt = smem_u32(&fwd_count_s);
+            uint32_t target = 0;
+            bool ok = true;
+            for (int w = first_work; w < p.total_work && ok; w += work_stride) {
+                const Work wk = decode_work(p, w);
+                target += kWorkerWarps;
+                if (smem_load_acquire(cnt) < target) {
+                    const uint64_t start = global_timer_ns();
+                    for (;;) {
+                        if (smem_load_acquire(cnt) >= target) break;
+                        if (*abort_flag) {
+                            ok = false;
+                            break;
+                        }
+                        if (global_timer_ns() - start > kWaitBudgetNs) {
+                            atomicOr(p.status, kStatForwarder);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(256);
+                    }
+                    if (!ok) break;
+                }
+                const int row0 = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM;
+                const int col0 = wk.nt * BN;
+                const long long boff = (long long)wk.b * p.strideC;
+                if (p.c_vec_ok && (p.N & 3) == 0) {
+                    constexpr int kC4 = BN / 4;              // 16-byte chunks per tile row
+                    constexpr int kPasses = kBM * kC4 / 64;  // chunks per forwarder thread
+                    static_assert(kPasses % 2 == 0, "the copy loop is unrolled by two");
+                    // (the control warps run on 40 registers: two chunks in flight per thread)
+#pragma unroll 1
+                    for (int i0 = 0; i0 < kPasses; i0 += 2) {
+                        const int u0 = ftid + i0 * 64, u1 = u0 + 64;
+                        const int r0 = row0 + u0 / kC4, c0 = col0 + (u0 % kC4) * 4;
+                        const int r1 = row0 + u1 / kC4, c1 = col0 + (u1 % kC4) * 4;
+                        const bool in0 = r0 < p.M && c0 < p.N, in1 = r1 < p.M && c1 < p.N;
+                        const long long off0 = boff + (long long)r0 * p.ldc + c0;
+                        const long long off1 = boff + (long long)r1 * p.ldc + c1;
+                        float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+                        if (in0) v0 = __ldcg(reinterpret_cast<const float4*>(p.dest[0] + off0));
+                        if (in1) v1 = __ldcg(reinterpret_cast<const float4*>(p.dest[0] + off1));
+#pragma unroll 1
+                        for (int dd = 1; dd < p.n_dest; ++dd) {
+                            float* dst = p.dest[dd];
+                            if (in0) *reinterpret_cast<float4*>(dst + off0) = v0;
+                            if (in1) *reinterpret_cast<float4*>(dst + off1) = v1;
+                        }
+                    }
+                } else {
+                    for (int u = ftid; u < kBM * BN; u += 64) {
+                        const int row = row0 + u / BN, col = col0 + u % BN;
+                        if (row < p.M && col < p.N) {
+                            const long long off = boff + (long long)row * p.ldc + col;
+                            const float v = __ldcg(p.dest[0] + off);
+                            for (int dd = 1; dd < p.n_dest; ++dd) p.dest[dd][off] = v;
+                        }
+                    }
+                }
+            }
         }
       }
     } else {
@@ -851,7 +904,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
         float acc[kCols];
         uint32_t it = 0, chain = 0;
         bool ok = true;
-        B200_PROF_DECL;
 
         // Convolution gathers: the k side of the addressing, once per CTA (see
         // conv_table_gather_split_store).
@@ -899,14 +951,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             const uint32_t buf = c & 1;
             bool got;
             {
-                B200_T0();
                 got = wait_bar(smem_u32(&accf_bar[buf]), (c >> 1) & 1, abort_flag, p.status,
                                kStatWorkerAcc);
                 got = __all_sync(0xffffffffu, got);
-                B200_T1(7);
             }
             if (!got) return false;
-            B200_T0();
             tc_fence_after_sync();
             const uint32_t t0 = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN +
                                 half * kCols;
@@ -929,7 +978,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) arrive_at_leader(smem_u32(&acce_bar[buf]));
-            B200_T1(8);
             return true;
         };
 
@@ -1017,51 +1065,56 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 if constexpr (kTma) {
                     bool got;
                     {
-                        B200_T0();
                         got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status,
                                        kStatWorkerFull);
                         got = __all_sync(0xffffffffu, got);
-                        B200_T1(5);
                     }
                     if (!got) {
                         ok = false;
                         break;
                     }
-                    B200_T0();
                     float4* hi = reinterpret_cast<float4*>(stage);
                     float4* lo = reinterpret_cast<float4*>(stage + Cfg::kHalf);
                     constexpr int kN4 = Cfg::kHalf / 16;
                     // TF32 mode without rounding: the tensor core reads the fp32 tile as it is
                     // (it drops the low 13 mantissa bits), so the workers only pass the stage on.
                     const int n4 = (prec3 || p.tf32_round) ? kN4 : 0;
+                    if (prec3 && p.trunc_hi) {
+                        // The raw tile stays as it is: the tensor core drops the low 13 mantissa bits
+                        // of what it reads, so its head is trunc(x); only the tail x - trunc(x)
+                        // (exact in fp32, then rounded to TF32) is written — one pass of
+                        // shared-memory stores instead of two.
 #pragma unroll 4
-                    for (int q = wtid; q < n4; q += kWorkerThreads) {
-                        const float4 x = hi[q];
-                        float4 h, l;
-                        tf32_split(x.x, h.x, l.x);
-                        tf32_split(x.y, h.y, l.y);
-                        tf32_split(x.z, h.z, l.z);
-                        tf32_split(x.w, h.w, l.w);
-                        hi[q] = h;
-                        if (prec3) lo[q] = l;
+                        for (int q = wtid; q < kN4; q += kWorkerThreads) {
+                            const float4 x = hi[q];
+                            lo[q] = make_float4(tf32_tail_of_truncated(x.x), tf32_tail_of_truncated(x.y),
+                                                tf32_tail_of_truncated(x.z), tf32_tail_of_truncated(x.w));
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int q = wtid; q < n4; q += kWorkerThreads) {
+                            const float4 x = hi[q];
+                            float4 h, l;
+                            tf32_split(x.x, h.x, l.x);
+                            tf32_split(x.y, h.y, l.y);
+                            tf32_split(x.z, h.z, l.z);
+                            tf32_split(x.w, h.w, l.w);
+                            hi[q] = h;
+                            if (prec3) lo[q] = l;
+                        }
                     }
-                    B200_T1(6);
                 } else {
                     bool got;
                     {
-                        B200_T0();
                         got = wait_bar(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status,
                                        kStatWorkerFull);
                         got = __all_sync(0xffffffffu, got);
-                        B200_T1(5);
                     }
                     if (!got) {
                         ok = false;
                         break;
                     }
-                    B200_T0();
                     ldg_phase(std::false_type{}, std::true_type{}, wk, wk.kb0 + i, stage);
-                    B200_T1(6);
                 }
                 // generic-proxy writes -> visible to the tensor core's async-proxy reads
                 fence_proxy_async_smem();
@@ -1090,7 +1143,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             ++chain;
 
             // ---------------------------------------------------------------- epilogue
-            B200_T0();
+            // Last tile of this CTA: what is left is the store, so the next kernel's set-up can run
+            // under it (it still waits for this kernel to complete before it touches memory).
+            if (w + work_stride >= p.total_work) grid_launch_dependents();
             // A thread holds kCols consecutive columns of ONE row; stored as it stands, every
             // store instruction of a warp would touch 32 different rows with 16 bytes each.
             // Each warp therefore turns 32 x 32 blocks through its own 4 KB of shared memory
@@ -1133,10 +1188,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const bool compact = split_out && p.tail_tiles > 0;
                 const long long ld_out = compact ? (long long)BN : split_out ? (long long)p.N : p.ldc;
                 const bool vec = compact ? true : split_out ? ((p.N & 3) == 0) : (p.c_vec_ok != 0);
-                const int n_out = split_out ? 1 : p.n_dest;
                 const bool fuse = !split_out && (p.bias != nullptr || p.addend != nullptr);
                 const bool relu = !split_out && p.relu != 0;
-                const bool plain = n_out == 1 && beta == 0.f;
+                const bool plain = beta == 0.f;
                 // compact: element (row, col) of tail tile t lives at
                 //   ((sp * tail_tiles + t) * kTileM + row - tile_row0) * BN + col - tile_col0
                 const long long base_off =
@@ -1233,8 +1287,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                                 if (col + 3 < p.N) v.w = add_bias_mask(p, v.w, row, col + 3);
                             }
                             const long long off = base_off + (long long)row * ld_out + col;
-                            for (int dd = 0; dd < n_out; ++dd) {
-                                float* dst = (split_out ? p.partial : p.dest[dd]) + off;
+                            {
+                                float* dst = (split_out ? p.partial : p.dest[0]) + off;
                                 if (vec && col + 3 < p.N) {
                                     float4 o = v;
                                     if (beta != 0.f) {
@@ -1268,9 +1322,16 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             }
-            B200_T1(9);
+            if constexpr (kConv == 0) {
+                // this warp's part of the tile is in C: the forwarders may copy it to the peers
+                if (p.n_dest > 1) {
+                    __syncwarp();
+                    if (lane == 0) smem_add_release(smem_u32(&fwd_count_s), 1u);
+                }
+            }
         }
-        B200_PROF_FLUSH(wtid == 0);
+        // The next kernel of the stream may start its set-up under this one's exit.
+        grid_launch_dependents();
     }
 
     tc_fence_before_sync();
@@ -1301,6 +1362,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict
                                      float* __restrict__ C, int split, long long batch, long long M,
                                      long long N, long long ldc, long long strideC, float alpha,
                                      float beta, int lanes) {
+    grid_dependency_wait();  // the partials come from the kernel before this one
     const long long total = batch * M * N;
     const int lane = threadIdx.x & 31;
     const int sub = lane & (lanes - 1);
@@ -1327,6 +1389,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p, const float* __restrict
 // Adds the compact split-K partials of the tail-wave tiles into C (ascending split order):
 // block x handles tile x / 8, rows [x % 8 * tile_rows / 8, ...).
 __global__ void tail_reduce_kernel(const GemmParams p, int tile_rows, int bn) {
+    grid_dependency_wait();  // the partials come from the kernel before this one
     const int tl = blockIdx.x >> 3;
     const int slab = blockIdx.x & 7;
     GemmParams q = p;
@@ -1384,6 +1447,26 @@ __global__ void conv_dw_reduce_kernel(const float* __restrict__ partial, int spl
             *out = s + (beta != 0.f ? beta * *out : 0.f);
         }
     }
+}
+
+// Test aid for the bounded waits: one warp waits, with the given budget, on a barrier that nobody
+// ever arrives at.  The wait runs out, records kStatSelfTest in *status and raises the abort flag —
+// the same path a lost TMA copy or tensor-core completion would take in the product kernels — and
+// the kernel returns normally.  Nothing here touches TMA or tensor memory.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long budget_ns, int* observed) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_s;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_s = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const bool got = wait_bar(smem_u32(&bar), 0, &abort_s, status, kStatSelfTest, budget_ns);
+    __syncthreads();
+    // observed[0]: threads whose wait returned "completed" (must be 0); observed[1]: the abort flag
+    if (got) atomicAdd(observed, 1);
+    if (threadIdx.x == 0) observed[1] = abort_s;
 }
 
 __global__ void scale_c_kernel(float* __restrict__ C, long long batch, long long M, long long N,

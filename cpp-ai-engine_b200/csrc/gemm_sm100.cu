@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <utility>
 
 namespace b200 {
 namespace {
@@ -35,6 +36,7 @@ struct DeviceState {
 };
 
 std::mutex g_mutex;
+std::mutex g_host_mutex[kMaxDevices];  // one b200_matmul_f32_host call per device at a time
 DeviceState g_dev[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
 
@@ -48,7 +50,12 @@ struct Options {
     long tail_split = 1;     // split the tiles of a mostly-empty last wave along K
     long group_m = 0;        // tile rows per scheduling band; 0 = automatic
     long tf32_round = 1;     // TF32 mode: round operands to nearest (1) or let the tensor core truncate (0)
+    long head_mode = 0;      // 3xTF32 head: 0 = rounded to nearest by the workers, 1 = the tensor core's truncation
+    long pdl = 1;            // launch with programmatic stream serialization (set-up overlaps the previous kernel)
+    long map_cache = 1;      // reuse encoded TMA tensor maps between calls
 };
+// Process-wide knobs, read without synchronisation on every call: set them while no other thread
+// is inside the library (they exist for benchmarking).
 Options g_opt;
 
 // k-blocks accumulated in TMEM before the partial sum is promoted to fp32 registers.  The
@@ -59,9 +66,6 @@ int promote_interval(int precision) {
     if (g_opt.promote_every >= 1) return static_cast<int>(g_opt.promote_every);
     return precision == B200_PRECISION_TF32 ? 8 : 1;
 }
-#ifdef B200_PHASE_PROFILE
-unsigned long long* g_prof = nullptr;  // development builds only
-#endif
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -164,6 +168,58 @@ int make_operand_map(OperandMap* om, const float* base, bool k_contig, int64_t r
     return r == CUDA_SUCCESS ? 0 : B200_EINVAL;
 }
 
+// A steady-state caller (a training step, a decode loop) issues the same products on the same
+// buffers again and again, and cuTensorMapEncodeTiled costs about a microsecond per operand — a
+// large part of what the host spends on an engine-sized product.  The encoded map depends only on
+// the arguments below (never on the buffer's contents), so each thread keeps the last maps it
+// encoded in a small direct-mapped table.
+struct MapKey {
+    const void* base;
+    int64_t rows_total, K, ld, batch_stride, batch;
+    int32_t k_contig, tile_rows, bk, dev;
+};
+struct MapSlot {
+    MapKey key;
+    OperandMap om;
+    bool valid;
+};
+constexpr int kMapSlots = 128;
+
+int cached_operand_map(OperandMap* om, const float* base, bool k_contig, int64_t rows_total, int64_t K,
+                       int64_t ld, int64_t batch_stride, int64_t batch, int tile_rows, int bk) {
+    if (!g_opt.map_cache)
+        return make_operand_map(om, base, k_contig, rows_total, K, ld, batch_stride, batch, tile_rows, bk);
+    thread_local MapSlot slots[kMapSlots] = {};
+    MapKey key;
+    std::memset(&key, 0, sizeof(key));  // padding bytes take part in the comparison
+    int dev = 0;
+    cudaGetDevice(&dev);
+    key.base = base;
+    key.rows_total = rows_total;
+    key.K = K;
+    key.ld = ld;
+    key.batch_stride = batch_stride;
+    key.batch = batch_stride ? batch : 1;
+    key.k_contig = k_contig ? 1 : 0;
+    key.tile_rows = tile_rows;
+    key.bk = bk;
+    key.dev = dev;
+    uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+    h ^= (static_cast<uint64_t>(rows_total) * 0xC2B2AE3D27D4EB4Full) ^ (static_cast<uint64_t>(K) << 21) ^
+         (static_cast<uint64_t>(ld) << 7) ^ static_cast<uint64_t>(tile_rows * 2 + key.k_contig);
+    MapSlot& slot = slots[(h >> 32) % kMapSlots];
+    if (slot.valid && std::memcmp(&slot.key, &key, sizeof(key)) == 0) {
+        *om = slot.om;
+        return 0;
+    }
+    int rc = make_operand_map(om, base, k_contig, rows_total, K, ld, batch_stride, batch, tile_rows, bk);
+    if (rc) return rc;
+    slot.key = key;
+    slot.om = *om;
+    slot.valid = true;
+    return 0;
+}
+
 bool tma_legal(const float* base, int64_t ld, int64_t batch_stride, int64_t batch) {
     if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
     if (ld & 3) return false;
@@ -172,31 +228,71 @@ bool tma_legal(const float* base, int64_t ld, int64_t batch_stride, int64_t batc
     return true;
 }
 
+// One launch through cudaLaunchKernelEx: optional cluster of two CTAs, and (option "pdl") the
+// programmatic-stream-serialization attribute, with which the kernel may become resident and run
+// its set-up (barriers, tensor-memory allocation, descriptor prefetch) while the previous kernel of
+// the stream drains; it executes griddepcontrol.wait before it touches global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                          int cluster, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(block), 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = static_cast<unsigned>(cluster);
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (g_opt.pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory, once per kernel and device.
+template <typename Kernel>
+int ensure_smem_attr(Kernel kernel, std::atomic<bool>* done, uint32_t bytes) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDevices) return B200_EDEVICE;
+    if (done[dev].load(std::memory_order_acquire)) return 0;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(bytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    done[dev].store(true, std::memory_order_release);
+    return 0;
+}
+
 template <int BN, int BK, bool kTma>
 int launch_cfg(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int grid,
                cudaStream_t stream) {
     using Cfg = TileCfg<BN, BK>;
     GemmParams p = params;
     fill_schedule(p);
-    static bool attr_set[kMaxDevices] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, BK, kTma>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(Cfg::kSmemBytes));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set[dev] = true;
-    }
-    gemm_tf32_kernel<BN, BK, kTma><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p, ma, mb);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return static_cast<int>(cudaGetLastError());
+    static std::atomic<bool> attr_set[kMaxDevices] = {};
+    if (int rc = ensure_smem_attr(gemm_tf32_kernel<BN, BK, kTma>, attr_set, Cfg::kSmemBytes)) return rc;
+    return static_cast<int>(launch_kernel(gemm_tf32_kernel<BN, BK, kTma>, grid, kThreads, Cfg::kSmemBytes,
+                                          stream, 1, p, ma, mb));
 }
 
 // CTA-pair kernel (tile 256 x 256): launched as clusters of two CTAs.
 int max_pair_clusters(int dev) {
-    static int cached[kMaxDevices] = {};
-    if (cached[dev] > 0) return cached[dev];
+    static std::atomic<int> cached[kMaxDevices] = {};
+    if (cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load(std::memory_order_relaxed);
+    std::lock_guard<std::mutex> lock(g_mutex);
     using Cfg = TileCfg<256, 32, true>;
     auto kernel = gemm_tf32_kernel<256, 32, true, true>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -220,7 +316,7 @@ int max_pair_clusters(int dev) {
         cudaGetLastError();
         return 0;
     }
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_release);
     return n;
 }
 
@@ -229,21 +325,8 @@ int launch_pair(const GemmParams& params, const CUtensorMap& ma, const CUtensorM
     using Cfg = TileCfg<256, 32, true>;
     GemmParams p = params;
     fill_schedule(p);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * clusters, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<256, 32, true, true>, p, ma, mb);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return static_cast<int>(e);
+    return static_cast<int>(launch_kernel(gemm_tf32_kernel<256, 32, true, true>, 2 * clusters, kThreads,
+                                          Cfg::kSmemBytes, stream, 2, p, ma, mb));
 }
 
 // Convolution kernels: register-staged loader with the implicit im2col gather (MODE 1 forward,
@@ -253,20 +336,11 @@ int launch_conv_cfg(const GemmParams& params, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN, 32>;
     GemmParams p = params;
     fill_schedule(p);
-    static bool attr_set[kMaxDevices] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
+    static std::atomic<bool> attr_set[kMaxDevices] = {};
     auto kernel = gemm_tf32_kernel<BN, 32, false, false, MODE>;
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(Cfg::kSmemBytes));
-        if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set[dev] = true;
-    }
+    if (int rc = ensure_smem_attr(kernel, attr_set, Cfg::kSmemBytes)) return rc;
     CUtensorMap unused{};
-    kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p, unused, unused);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_kernel(kernel, grid, kThreads, Cfg::kSmemBytes, stream, 1, p, unused, unused));
 }
 
 int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
@@ -375,6 +449,7 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     bool pair = false;
     int auto_parts = 0;  // K-split chosen together with the tile (0: tile forced by option)
     const int64_t kblocks = ceil_div(K, 32);
+    const size_t out_bytes = static_cast<size_t>(batch) * M * N * sizeof(float);  // one partial matrix
     const bool pair_legal = pl.tma && pl.bk == 32 && M > kBM && g_opt.pair_mode != 1;
     if (g_opt.tile_n == 32 || g_opt.tile_n == 64 || g_opt.tile_n == 128 || g_opt.tile_n == 256) {
         bn = static_cast<int>(g_opt.tile_n);
@@ -421,10 +496,12 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
             // deterministic split-K: few tiles, a k-loop worth cutting, room for the partials
             if (!cand_pair[i] && g_opt.split_k == 0 && tiles * 2 <= units && kblocks >= 8) {
                 int64_t p2 = std::min<int64_t>(units / tiles, kblocks / 4);
+                // a workspace too small for that many partial matrices still allows a shallower split
+                p2 = std::min<int64_t>(p2, static_cast<int64_t>(std::min<size_t>(workspace_bytes / out_bytes, 1u << 20)));
+                if (p2 < 1) p2 = 1;
                 const int64_t per = (kblocks + p2 - 1) / p2;
                 p2 = (kblocks + per - 1) / per;
-                if (p2 > 1 && static_cast<size_t>(p2) * batch * M * N * sizeof(float) <= workspace_bytes &&
-                    time_of(p2) < t) {
+                if (p2 > 1 && static_cast<size_t>(p2) * out_bytes <= workspace_bytes && time_of(p2) < t) {
                     parts = p2;
                     t = time_of(p2);
                 }
@@ -457,6 +534,10 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
         if (want > pl.kblocks / 4) want = pl.kblocks / 4;
     }
     if (want > pl.kblocks) want = pl.kblocks;
+    if (g_opt.split_k == 0 && want > 1) {  // automatic: as deep a split as the workspace holds
+        const size_t fit = workspace_bytes / out_bytes;
+        if (static_cast<size_t>(want) > fit) want = static_cast<int>(fit);
+    }
     if (want > 1) {
         const int per = ceil_div(pl.kblocks, want);
         const int split = ceil_div(pl.kblocks, per);
@@ -577,6 +658,7 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     p.precision = precision;
     p.promote_every = promote_interval(precision);
     p.tf32_round = g_opt.tf32_round ? 1 : 0;
+    p.trunc_hi = g_opt.head_mode == 1 ? 1 : 0;
     p.partial = static_cast<float*>(workspace);
     p.status = st.status;
     if (ep != nullptr) {
@@ -585,9 +667,6 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         p.ld_addend = ep->ld_addend;
         p.relu = ep->relu;
     }
-#ifdef B200_PHASE_PROFILE
-    p.prof = g_prof;
-#endif
     p.a_vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (lda & 3) == 0 &&
                   (strideA & 3) == 0)
                      ? 1
@@ -606,9 +685,9 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     if (pl.tma) {
         int rc = resolve_encoder();
         if (rc) return rc;
-        rc = make_operand_map(&oa, A, a_k_contig, M, K, lda, strideA, batch, kBM, pl.bk);
+        rc = cached_operand_map(&oa, A, a_k_contig, M, K, lda, strideA, batch, kBM, pl.bk);
         if (rc) return rc;
-        rc = make_operand_map(&ob, B, b_k_contig, N, K, ldb, strideB, batch,
+        rc = cached_operand_map(&ob, B, b_k_contig, N, K, ldb, strideB, batch,
                               pl.pair ? pl.bn / 2 : pl.bn, pl.bk);
         if (rc) return rc;
         p.a_lbo = oa.lbo;
@@ -654,9 +733,8 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         rc = launch(q);
         if (rc) return rc;
         fill_schedule(q);
-        tail_reduce_kernel<<<pl.tail_tiles * 8, 256, 0, stream>>>(q, pl.pair ? 2 * kBM : kBM, pl.bn);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        rc = static_cast<int>(cudaGetLastError());
+        rc = static_cast<int>(launch_kernel(tail_reduce_kernel, pl.tail_tiles * 8, 256, 0, stream, 1, q,
+                                            pl.pair ? 2 * kBM : kBM, pl.bn));
         if (rc) return rc;
     }
     if (pl.split_k > 1) {
@@ -668,11 +746,11 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         while (lanes < 32 && lanes * 2 <= pl.split_k && elems * lanes * 2 <= max_threads) lanes *= 2;
         int blocks = static_cast<int>((elems * lanes + 255) / 256);
         if (blocks > st.sm_count * 8) blocks = st.sm_count * 8;
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p, static_cast<const float*>(workspace), C,
-                                                         pl.split_k, batch, M, N, ldc, strideC,
-                                                         alpha, beta, lanes);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        rc = static_cast<int>(cudaGetLastError());
+        rc = static_cast<int>(launch_kernel(splitk_reduce_kernel, blocks, 256, 0, stream, 1, p,
+                                            static_cast<const float*>(workspace), C, pl.split_k,
+                                            static_cast<long long>(batch), static_cast<long long>(M),
+                                            static_cast<long long>(N), static_cast<long long>(ldc),
+                                            static_cast<long long>(strideC), alpha, beta, lanes));
     }
     return rc;
 }
@@ -839,14 +917,19 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+// For the sharding layer (shard_sm100.cu): the current device's status word and the launch counter.
+int* device_status_word(int* rc) {
+    DeviceState* st = nullptr;
+    *rc = device_state(&st);
+    return *rc ? nullptr : st->status;
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" {
-
-#ifdef B200_PHASE_PROFILE
-// Development builds only: device array of 12 cycle counters filled by CTA 0.
-void b200_dev_set_profile_buffer(unsigned long long* buf) { g_prof = buf; }
-#endif
 
 int b200_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
                   int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
@@ -892,6 +975,27 @@ size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K) {
     return static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float);
 }
 
+int b200_gemm_f32_plan(int64_t batch, int64_t M, int64_t N, int64_t K, size_t workspace_bytes,
+                       b200_plan_info* out) {
+    if (out == nullptr || batch <= 0 || M <= 0 || N <= 0 || K <= 0) return B200_EINVAL;
+    DeviceState tmp;
+    DeviceState* st = nullptr;
+    if (device_state(&st) != 0) {
+        tmp.sm_count = 148;
+        st = &tmp;
+    }
+    const Plan pl = make_plan(*st, batch, M, N, K, true, workspace_bytes);
+    out->tile_n = pl.bn;
+    out->pair = pl.pair ? 1 : 0;
+    out->split_k = pl.split_k;
+    out->tail_tiles = pl.tail_tiles;
+    out->tail_split = pl.tail_tiles > 0 ? pl.tail_split : 1;
+    out->kernels = 1 + (pl.split_k > 1 ? 1 : 0) + (pl.tail_tiles > 0 ? 2 : 0);
+    out->workspace_used = pl.split_k > 1 ? static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float)
+                                         : pl.tail_bytes;
+    return B200_OK;
+}
+
 int b200_matmul_f32(const float* a, const float* b, float* out, size_t batch, size_t rows,
                     size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta,
                     void* workspace, size_t workspace_bytes, void* stream) {
@@ -915,6 +1019,11 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
     const size_t nws = b200_gemm_f32_workspace(static_cast<int64_t>(batch), static_cast<int64_t>(rows),
                                                static_cast<int64_t>(cols),
                                                static_cast<int64_t>(inner_dim));
+    // The staging buffers, streams and events are per device and shared by every caller: a second
+    // thread calling on the same device waits here until the first call has returned.
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> host_lock(g_host_mutex[dev]);
     {
         std::lock_guard<std::mutex> lock(g_mutex);
         if ((rc = grow(reinterpret_cast<void**>(&st->stage_a), &st->cap_a, na ? na : 16))) return rc;
@@ -925,8 +1034,15 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
     // Large single products overlap their transfers with the math, block by block.
     if (batch == 1 && beta == 0.0f && rows >= 4096 && cols >= 4096 && inner_dim >= 512 &&
         (cols % 4) == 0 && (inner_dim % 4) == 0 && g_opt.host_pipeline != 0) {
-        return host_wavefront(*st, a, b, out, static_cast<int64_t>(rows), static_cast<int64_t>(inner_dim),
-                              static_cast<int64_t>(cols));
+        rc = host_wavefront(*st, a, b, out, static_cast<int64_t>(rows), static_cast<int64_t>(inner_dim),
+                            static_cast<int64_t>(cols));
+        if (rc != B200_OK && st->pipe_ready) {
+            // leave no copy from or to the caller's buffers in flight behind an error return
+            cudaStreamSynchronize(st->s_h2d);
+            cudaStreamSynchronize(st->s_comp);
+            cudaStreamSynchronize(st->s_d2h);
+        }
+        return rc;
     }
     cudaStream_t stream = nullptr;
     cudaError_t e;
@@ -1070,9 +1186,6 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
     base.cv_ow = static_cast<int>(ow);
     base.cv_oc = static_cast<int>(out_c);
     base.cv_ones_col = -1;
-#ifdef B200_PHASE_PROFILE
-    base.prof = g_prof;
-#endif
 
     // The bias sums ride along with the weight gradient as one more column (dOut^T x ones) whenever
     // that product is split; otherwise they have a small kernel of their own.
@@ -1249,11 +1362,6 @@ uint32_t attention_bwd_layout(b200::AttnBwdParams& p) {
 
 extern "C" {
 
-#ifdef B200_ATTN_PROFILE
-static long long* g_attn_prof = nullptr;
-void b200_dev_set_attn_prof(long long* buf) { g_attn_prof = buf; }
-#endif
-
 int b200_attention_f32_strided(const float* q, const float* k, const float* v, const float* mask,
                                float* out, float* weights, int64_t batch, int64_t heads, int64_t s_q,
                                int64_t s_k, int64_t d_k, int64_t d_v, const int64_t q_strides[3],
@@ -1296,9 +1404,6 @@ int b200_attention_f32_strided(const float* q, const float* k, const float* v, c
     p.scale = scale;
     p.precision = precision;
     p.status = st->status;
-#ifdef B200_ATTN_PROFILE
-    p.prof = g_attn_prof;
-#endif
     const uint32_t q_bytes = 128u * p.dk_pad * 4u, k_bytes = static_cast<uint32_t>(p.sk_pad) * p.dk_pad * 4u;
     const uint32_t p_bytes = 128u * p.sk_pad * 4u, v_bytes = static_cast<uint32_t>(p.dv_pad) * p.sk_pad * 4u;
     const uint32_t region1 = std::max(2 * (q_bytes + k_bytes), 2 * p_bytes);
@@ -1424,16 +1529,17 @@ int b200_gemm_f32_static_scratch(const float* A, const float* B, float* C, int64
     if (C == nullptr) return B200_EINVAL;
     if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
     if (batch == 1 && strideC == 0) strideC = M * ldc;
-    // The same plan the allocating entry point would make with ample workspace; refuse what
-    // the fixed scratch cannot hold rather than silently running a different plan.
-    if (batch > 0 && M > 0 && N > 0 && K > 0) {
-        const bool tma_ok = A != nullptr && B != nullptr && tma_legal(A, lda, strideA, batch) &&
-                            tma_legal(B, ldb, strideB, batch);
-        const Plan pl = make_plan(ss->st, batch, M, N, K, tma_ok, static_cast<size_t>(-1));
-        if (pl.split_k > 1) {
-            const size_t need = static_cast<size_t>(pl.split_k) * batch * M * N * sizeof(float);
-            if (need > kStaticScratchBytes) return B200_ENOSPACE;
-        }
+    // The plan is the one b200_gemm_f32 makes when it is handed 4 MiB of workspace: the automatic
+    // K-split is as deep as the fixed scratch holds (possibly not split at all), and a last wave
+    // whose K-split partials do not fit runs unsplit.  Only a split that the caller FORCED through
+    // the "split_k" option and that does not fit is refused: there is no honest way to run it.
+    if (batch > 0 && M > 0 && N > 0 && K > 0 && g_opt.split_k > 1) {
+        const int64_t kblocks = (K + 31) / 32;
+        const int64_t want = std::min<int64_t>(g_opt.split_k, kblocks);
+        const int64_t per = (kblocks + want - 1) / want;
+        const int64_t split = (kblocks + per - 1) / per;
+        const size_t one = static_cast<size_t>(batch) * M * N * sizeof(float);
+        if (split > 1 && one > kStaticScratchBytes / static_cast<size_t>(split)) return B200_ENOSPACE;
     }
     DeviceState st = ss->st;  // plain copy: holds no allocation
     if (device_status != nullptr) st.status = device_status;
@@ -1452,9 +1558,47 @@ int b200_gemm_status(void) {
     int word = 0;
     if ((e = cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
         return static_cast<int>(e);
-    if (word != 0) {
-        cudaMemset(st->status, 0, sizeof(int));
-        return B200_ETIMEDOUT;
+    if (word != 0) cudaMemset(st->status, 0, sizeof(int));
+    // the word inside the library's device image that b200_gemm_f32_static_scratch reports to when
+    // its caller passed no status pointer (its address is known once that entry point has run here)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int* static_word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (dev >= 0 && dev < kMaxDevices && g_static[dev].ready) static_word = g_static[dev].st.status;
+    }
+    if (static_word != nullptr) {
+        int w2 = 0;
+        if ((e = cudaMemcpy(&w2, static_word, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+            return static_cast<int>(e);
+        if (w2 != 0) cudaMemset(static_word, 0, sizeof(int));
+        word |= w2;
+    }
+    return word != 0 ? B200_ETIMEDOUT : B200_OK;
+}
+
+int b200_gemm_selftest_timeout(unsigned budget_us, int* observed_host) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    if (budget_us == 0 || budget_us > 100000) return B200_EINVAL;  // at most 0.1 s
+    int* observed = nullptr;
+    cudaError_t e = cudaMalloc(&observed, 2 * sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaMemset(observed, 0, 2 * sizeof(int));
+    wait_timeout_selftest_kernel<<<1, 32>>>(st->status, static_cast<unsigned long long>(budget_us) * 1000ull,
+                                            observed);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    int host[2] = {0, 0};
+    if (e == cudaSuccess) e = cudaMemcpy(host, observed, sizeof(host), cudaMemcpyDeviceToHost);
+    cudaFree(observed);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (observed_host != nullptr) {
+        observed_host[0] = host[0];
+        observed_host[1] = host[1];
     }
     return B200_OK;
 }
@@ -1488,6 +1632,13 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "pair_mode")) {
         if (value < 0 || value > 2) return B200_EINVAL;
         g_opt.pair_mode = value;
+    } else if (!std::strcmp(name, "head_mode")) {
+        if (value < 0 || value > 1) return B200_EINVAL;
+        g_opt.head_mode = value;
+    } else if (!std::strcmp(name, "pdl")) {
+        g_opt.pdl = value ? 1 : 0;
+    } else if (!std::strcmp(name, "map_cache")) {
+        g_opt.map_cache = value ? 1 : 0;
     } else {
         return B200_EINVAL;
     }

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use:
-// mbarrier, TMA tiled loads, tcgen05 (TMEM allocation, MMA, commit, ld/st) and
+// mbarrier, TMA tiled loads, tcgen05 (TMEM allocation, MMA, commit, ld) and
 // the shared-memory / instruction descriptors that tcgen05.mma consumes.
 //
 // Everything here is device-only and header-only.  Every wait is bounded by
@@ -25,6 +25,34 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+// ---------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may become resident
+// while the kernel before it in the stream is still running.  grid_dependency_wait() returns once
+// that earlier kernel has completed and its memory is visible: nothing that it may have written
+// (or may still read) is touched before this call.  Without the attribute both are no-ops.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel of the stream (if it was launched with the attribute) start its own
+// set-up; it still waits for this kernel's completion before it touches memory.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
+// a monotone counter in shared memory (release add / acquire load, CTA scope)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void smem_add_release(uint32_t addr, uint32_t v) {
+    asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_load_acquire(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
 }
 
 // ---------------------------------------------------------------------------
@@ -151,16 +179,6 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
 
 // x is the innermost (contiguous) coordinate and must keep x * 4 bytes a
 // multiple of 16.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map,
-                                            uint32_t bar, int32_t x, int32_t y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];"
-        :
-        : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map,
                                             uint32_t bar, int32_t x, int32_t y, int32_t z) {
     asm volatile(
@@ -214,10 +232,8 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // tcgen05: descriptors
 // ---------------------------------------------------------------------------
 // Swizzle / layout-type codes of the shared-memory matrix descriptor (bits 61..63).
-constexpr uint32_t kLayoutNone = 0;
 constexpr uint32_t kLayoutSw128 = 2;
 constexpr uint32_t kLayoutSw64 = 4;
-constexpr uint32_t kLayoutSw32 = 6;
 
 // 64-bit shared-memory matrix descriptor.
 //   bits  0..13  start address >> 4
@@ -270,20 +286,6 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem]; A is K-major in TMEM (row = lane, k = column).
-__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
-        "}\n"
-        :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
 // Pair form: one thread of the leader CTA issues an M = 256 product; each CTA of the pair
 // supplies 128 rows of A and half of the columns of B from the SAME shared-memory offsets,
 // and receives 128 rows of D in its own TMEM.
@@ -321,15 +323,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 // ---------------------------------------------------------------------------
 // tcgen05: TMEM <-> registers (32 lanes x 32 bit, warp w touches lanes 32*(w%4)..+31)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7])
-        : "r"(taddr)
-        : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -359,19 +352,6 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-        :
-        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-          "r"(r[7])
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_wait() {
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
 // ---------------------------------------------------------------------------
 // TF32 split used by the error-compensated ("3xTF32") product
 // ---------------------------------------------------------------------------
@@ -386,6 +366,13 @@ __host__ __device__ __forceinline__ uint32_t tf32_round_bits(uint32_t x) {
 __device__ __forceinline__ void tf32_split(float x, float& hi, float& lo) {
     hi = __uint_as_float(tf32_round_bits(__float_as_uint(x)));
     lo = __uint_as_float(tf32_round_bits(__float_as_uint(x - hi)));
+}
+
+// The tail that goes with a head the tensor core makes itself by truncation:
+// x = trunc_tf32(x) + t exactly; returns t rounded to TF32 (|t| < 2^-10 |x|, error <= 2^-21 |x|).
+__device__ __forceinline__ float tf32_tail_of_truncated(float x) {
+    const float head = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    return __uint_as_float(tf32_round_bits(__float_as_uint(x - head)));
 }
 
 }  // namespace b200

@@ -29,11 +29,21 @@ EXPORTS = (
     "b200_conv2d_backward_f32",
     "b200_gemm_f32_fused",
     "b200_gemm_f32_workspace",
+    "b200_gemm_f32_plan",
     "b200_matmul_f32",
     "b200_matmul_f32_host",
     "b200_gemm_f32_colshard",
+    "b200_shard_comm_create",
+    "b200_shard_comm_set_peers",
+    "b200_shard_comm_set_nccl",
+    "b200_shard_comm_destroy",
+    "b200_shard_columns",
+    "b200_gemm_f32_sharded",
+    "b200_shard_host_plan",
+    "b200_matmul_f32_host_sharded",
     "b200_gemm_f32_static_scratch",
     "b200_gemm_status",
+    "b200_gemm_selftest_timeout",
     "b200_gemm_launch_count",
     "b200_gemm_set_option",
     "b200_gemm_strerror",
@@ -44,6 +54,18 @@ class Epilogue(ctypes.Structure):
     """``b200_epilogue``: bias[N], addend[M x N] (shared across the batch), relu flag."""
     _fields_ = [("bias", ctypes.c_void_p), ("addend", ctypes.c_void_p), ("ld_addend", ctypes.c_int64),
                 ("relu", ctypes.c_int)]
+
+
+class PlanInfo(ctypes.Structure):
+    """``b200_plan_info``: what one call of ``b200_gemm_f32`` would launch."""
+    _fields_ = [("tile_n", ctypes.c_int), ("pair", ctypes.c_int), ("split_k", ctypes.c_int),
+                ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int), ("kernels", ctypes.c_int),
+                ("workspace_used", ctypes.c_size_t)]
+
+
+class ShardHostLayout(ctypes.Structure):
+    """``b200_shard_host_layout``: how the rows of A are cut for the sharded host-buffer product."""
+    _fields_ = [("chunks", ctypes.c_int), ("rows_per_rank", ctypes.c_int64), ("chunk_rows", ctypes.c_int64)]
 
 
 class B200Error(RuntimeError):
@@ -94,6 +116,8 @@ def load() -> ctypes.CDLL:
     lib.b200_conv2d_backward_f32.argtypes = [c_vp] * 6 + [c_i64] * 9 + [c_f, c_int, c_vp, c_sz, c_vp]
     lib.b200_gemm_f32_workspace.restype = c_sz
     lib.b200_gemm_f32_workspace.argtypes = [c_i64, c_i64, c_i64, c_i64]
+    lib.b200_gemm_f32_plan.restype = c_int
+    lib.b200_gemm_f32_plan.argtypes = [c_i64, c_i64, c_i64, c_i64, c_sz, ctypes.POINTER(PlanInfo)]
     lib.b200_matmul_f32.restype = c_int
     lib.b200_matmul_f32.argtypes = [c_vp, c_vp, c_vp, c_sz, c_sz, c_sz, c_sz, c_int, c_int, c_f,
                                     c_vp, c_sz, c_vp]
@@ -102,12 +126,31 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_f32_colshard.restype = c_int
     lib.b200_gemm_f32_colshard.argtypes = [c_vp, c_vp, ctypes.POINTER(c_vp), c_int, c_i64, c_i64,
                                            c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_vp]
+    lib.b200_shard_comm_create.restype = c_int
+    lib.b200_shard_comm_create.argtypes = [ctypes.POINTER(c_vp), c_int, c_int]
+    lib.b200_shard_comm_set_peers.restype = c_int
+    lib.b200_shard_comm_set_peers.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
+    lib.b200_shard_comm_set_nccl.restype = c_int
+    lib.b200_shard_comm_set_nccl.argtypes = [c_vp, c_vp]
+    lib.b200_shard_comm_destroy.restype = c_int
+    lib.b200_shard_comm_destroy.argtypes = [c_vp]
+    lib.b200_shard_columns.restype = None
+    lib.b200_shard_columns.argtypes = [c_i64, c_int, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]
+    lib.b200_gemm_f32_sharded.restype = c_int
+    lib.b200_gemm_f32_sharded.argtypes = [c_vp, c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64,
+                                          c_int, c_vp]
+    lib.b200_shard_host_plan.restype = c_int
+    lib.b200_shard_host_plan.argtypes = [c_i64, c_int, c_int, ctypes.POINTER(ShardHostLayout)]
+    lib.b200_matmul_f32_host_sharded.restype = c_int
+    lib.b200_matmul_f32_host_sharded.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int]
     lib.b200_gemm_f32_static_scratch.restype = c_int
     lib.b200_gemm_f32_static_scratch.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
                                                  c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f, c_f,
                                                  c_int, c_vp, c_vp]
     lib.b200_gemm_status.restype = c_int
     lib.b200_gemm_status.argtypes = []
+    lib.b200_gemm_selftest_timeout.restype = c_int
+    lib.b200_gemm_selftest_timeout.argtypes = [ctypes.c_uint, ctypes.POINTER(c_int)]
     lib.b200_gemm_launch_count.restype = ctypes.c_uint64
     lib.b200_gemm_launch_count.argtypes = []
     lib.b200_gemm_set_option.restype = c_int
@@ -130,7 +173,9 @@ def _stream_ptr(stream) -> int:
     if stream is None:
         import torch
 
-        return int(torch.cuda.current_stream().cuda_stream)
+        # the raw handle of torch's current stream on the current device (no Stream object is built:
+        # this runs once per product, and an engine-sized product is a few microseconds)
+        return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
     if isinstance(stream, int):
         return stream
     return int(stream.cuda_stream)
@@ -241,6 +286,13 @@ def workspace_bytes(batch: int, M: int, N: int, K: int) -> int:
     return int(load().b200_gemm_f32_workspace(batch, M, N, K))
 
 
+def plan(batch: int, M: int, N: int, K: int, workspace_bytes: int = 2 ** 62) -> dict:
+    """The tile, K-split and kernel count ``gemm`` would use for this shape and workspace."""
+    info = PlanInfo()
+    _check(load().b200_gemm_f32_plan(batch, M, N, K, workspace_bytes, ctypes.byref(info)), "b200_gemm_f32_plan")
+    return {name: int(getattr(info, name)) for name, _ in PlanInfo._fields_}
+
+
 def matmul_host(a, b, out, *, batch: int, rows: int, inner: int, cols: int, a_batched: bool,
                 b_batched: bool, beta: float = 0.0) -> None:
     """Host-buffer product (numpy float32 arrays): upload, kernel, download, synchronised."""
@@ -258,9 +310,81 @@ def gemm_colshard(A, B, dest: Sequence, *, M: int, N: int, K: int, col0: int, co
     _check(rc, "b200_gemm_f32_colshard")
 
 
+SHARD_FUSED = 0
+SHARD_NCCL = 1
+
+
+class ShardComm:
+    """``b200_shard_comm``: the handle of the sharded products (one per rank, on the current device)."""
+
+    def __init__(self, rank: int, world: int):
+        self._h = ctypes.c_void_p()
+        _check(load().b200_shard_comm_create(ctypes.byref(self._h), rank, world), "b200_shard_comm_create")
+        self.rank, self.world = rank, world
+
+    def set_peers(self, c_bufs: Sequence, flags: Sequence) -> None:
+        """Every rank's C buffer and zeroed flag block (tensors or device addresses, index = rank)."""
+        arr_c = (ctypes.c_void_p * self.world)(*[_ptr(t) for t in c_bufs])
+        arr_f = (ctypes.c_void_p * self.world)(*[_ptr(t) for t in flags])
+        _check(load().b200_shard_comm_set_peers(self._h, arr_c, arr_f), "b200_shard_comm_set_peers")
+
+    def set_nccl(self, comm_ptr: int) -> None:
+        """The caller's ``ncclComm_t`` of the same ranks, as an integer address."""
+        _check(load().b200_shard_comm_set_nccl(self._h, ctypes.c_void_p(comm_ptr)), "b200_shard_comm_set_nccl")
+
+    def close(self) -> None:
+        if self._h:
+            load().b200_shard_comm_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def shard_columns(N: int, world: int, rank: int):
+    """``b200_shard_columns``: the (col0, cols) of a rank, as the library computes them."""
+    c0, c = ctypes.c_int64(), ctypes.c_int64()
+    load().b200_shard_columns(N, world, rank, ctypes.byref(c0), ctypes.byref(c))
+    return int(c0.value), int(c.value)
+
+
+def shard_host_plan(M: int, world: int, chunks: int = 0) -> dict:
+    """``b200_shard_host_plan``: chunks, rows per rank and rows per chunk of the sharded host product."""
+    lay = ShardHostLayout()
+    _check(load().b200_shard_host_plan(M, world, chunks, ctypes.byref(lay)), "b200_shard_host_plan")
+    return {"chunks": int(lay.chunks), "rows_per_rank": int(lay.rows_per_rank), "chunk_rows": int(lay.chunk_rows)}
+
+
+def gemm_sharded(comm: ShardComm, mode: int, A, B, C, *, M: int, N: int, K: int, lda: int, ldb: int, ldc: int,
+                 precision: int = PRECISION_3XTF32, stream=None) -> None:
+    """``C = A @ B`` column-sharded over the ranks of ``comm``; every rank ends with all of C."""
+    rc = load().b200_gemm_f32_sharded(comm._h, mode, _ptr(A), _ptr(B), _ptr(C), M, N, K, lda, ldb, ldc, precision,
+                                      _stream_ptr(stream))
+    _check(rc, "b200_gemm_f32_sharded")
+
+
+def matmul_host_sharded(comm: ShardComm, a_rows, b_cols, c_cols, *, M: int, N: int, K: int, chunks: int = 0) -> None:
+    """The sharded product from host buffers (numpy float32 arrays: this rank's rows of A, its columns
+    of B, its columns of C); returns when the result is on the host."""
+    rc = load().b200_matmul_f32_host_sharded(comm._h, a_rows.ctypes.data, b_cols.ctypes.data, c_cols.ctypes.data,
+                                             M, N, K, chunks)
+    _check(rc, "b200_matmul_f32_host_sharded")
+
+
 def status() -> None:
     """Synchronises the current device and raises if a bounded device-side wait ran out."""
     _check(load().b200_gemm_status(), "b200_gemm_status")
+
+
+def selftest_timeout(budget_us: int = 1000):
+    """Makes one bounded device-side wait run out on purpose (nothing faults).  Returns
+    ``(threads_that_wrongly_completed, abort_flag)``; :func:`status` raises once afterwards."""
+    seen = (ctypes.c_int * 2)(-1, -1)
+    _check(load().b200_gemm_selftest_timeout(int(budget_us), seen), "b200_gemm_selftest_timeout")
+    return int(seen[0]), int(seen[1])
 
 
 def launch_count() -> int:

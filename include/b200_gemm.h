@@ -23,6 +23,20 @@
  * every few k-steps, so results stay at fp32-level accuracy.  B200_PRECISION_TF32 is the
  * opt-in single-product mode (about 1e-3 relative error, like the reference's own
  * MatmulKernel::TensorCore, include/engine/cuda.hpp:153-177) and is never the default.
+ *
+ * Finite inputs only.  The reference's CPU loop skips every term whose A value is exactly zero
+ * (src/tensor_ops.cpp:555), so it never forms 0 * Inf or 0 * NaN; for finite inputs the skip
+ * changes nothing, and zeros in A give the same results here as there.  An infinite or NaN input,
+ * however, turns the affected outputs into NaN here (the split forms Inf - Inf), where the
+ * reference yields +-Inf or leaves rows with a zero A value untouched.  Callers that may hold
+ * non-finite values must clean them first.
+ *
+ * Threads.  Like the reference's device layer (one dispatching thread, src/cuda/runtime.cu:159-160)
+ * the library expects one thread per device to issue products.  Calls from several threads are
+ * safe as far as the library's own state goes (first-use set-up is locked, and
+ * b200_matmul_f32_host admits one call per device at a time), but b200_gemm_set_option changes
+ * process-wide knobs without synchronisation: set options while no other thread is inside the
+ * library.
  */
 #ifndef B200_GEMM_H
 #define B200_GEMM_H
@@ -181,6 +195,19 @@ int b200_attention_backward_f32_strided(const float* q, const float* k, const fl
  * (src/cuda/kernels_matmul.cu:866-893, src/cuda/kernels.cu:593-604). */
 size_t b200_gemm_f32_workspace(int64_t batch, int64_t M, int64_t N, int64_t K);
 
+/* What b200_gemm_f32 would do with TMA-legal operands of this shape and `workspace_bytes` of
+ * workspace: the tile width, whether tiles run on CTA pairs, the deterministic K-split (1 = none;
+ * as deep as the workspace holds, never deeper than the planner wants), the K-split of a mostly
+ * empty last wave, the kernels one call launches and the workspace bytes it writes.  Works
+ * without a device (148 SMs are assumed then).  The counterpart of the reference's
+ * resolve_matmul_kernel (src/cuda/runtime.cu:293-298) made visible to callers and tests. */
+typedef struct b200_plan_info {
+    int tile_n, pair, split_k, tail_tiles, tail_split, kernels;
+    size_t workspace_used;
+} b200_plan_info;
+int b200_gemm_f32_plan(int64_t batch, int64_t M, int64_t N, int64_t K, size_t workspace_bytes,
+                       b200_plan_info* out);
+
 /* The reference seam itself, argument for argument (include/engine/detail/cuda_ops.hpp:46-47):
  * out = a x b + beta * out over `batch` contiguous row-major matrices, a is (rows x inner_dim),
  * b is (inner_dim x cols); an unbatched operand is reused for every batch element. */
@@ -203,12 +230,88 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
  * [col0, col0 + cols) of C = A x B from its full A (M x K, lda) and the same columns of the full
  * B (K x N, ldb), and stores every finished tile at the same position of each of the
  * n_dest row-major M x N buffers in dest[] (host array of DEVICE pointers: this rank's own C
- * and, for the fused all-gather, the peers' C mapped into this process).  Plain stores over
- * NVLink; no multicast.  Callers order completion across ranks themselves (a barrier after the
- * stream is idle). */
+ * first and, for the fused all-gather, the peers' C mapped into this process): the worker warps
+ * store each tile into dest[0], two otherwise idle warps copy it on to dest[1..].  Plain stores over
+ * NVLink; no multicast.  This is the building block of b200_gemm_f32_sharded, which adds the
+ * barriers: called directly, the caller orders it across ranks itself — before (a peer must be done
+ * reading the C this call overwrites) and after (a barrier once the stream is idle). */
 int b200_gemm_f32_colshard(const float* A, const float* B, float* const* dest, int n_dest,
                            int64_t M, int64_t N, int64_t K, int64_t col0, int64_t cols, int64_t lda,
                            int64_t ldb, int64_t ldc, int precision, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The sharded product behind one handle (no reference counterpart, src/cuda/runtime.cu:83).
+ *
+ * One rank per GPU of one node — a process per GPU, or one thread per GPU in one process; never two
+ * ranks on one GPU (the barrier kernels of the ranks wait for one another).  A communicator belongs
+ * to the device that was current when it was created, holds no pointer it owns except its own
+ * staging buffers, and is used by one thread at a time.
+ *
+ *   b200_shard_comm_create     rank in [0, world), world <= 8.
+ *   b200_shard_comm_set_peers  enables B200_SHARD_FUSED.  c_bufs[r]: rank r's full M x N result buffer
+ *                              and flags[r]: rank r's block of `world` 32-bit words, both as DEVICE
+ *                              pointers valid in THIS process (own memory at [rank]; the peers' through
+ *                              peer access inside one process, or CUDA IPC / symmetric memory between
+ *                              processes).  Every flag block must be zero before the first call and is
+ *                              owned by the library from then on.
+ *   b200_shard_comm_set_nccl   enables B200_SHARD_NCCL and b200_matmul_f32_host_sharded.  nccl_comm is the
+ *                              caller's ncclComm_t of the same ranks; the library resolves NCCL at run
+ *                              time from the libnccl.so.2 already in the process (else the system's)
+ *                              and has no link-time dependency on it.  B200_EDEVICE if none is found.
+ */
+typedef struct b200_shard_comm b200_shard_comm;
+int b200_shard_comm_create(b200_shard_comm** comm, int rank, int world);
+int b200_shard_comm_set_peers(b200_shard_comm* comm, float* const* c_bufs, uint32_t* const* flags);
+int b200_shard_comm_set_nccl(b200_shard_comm* comm, void* nccl_comm);
+int b200_shard_comm_destroy(b200_shard_comm* comm);
+
+/* The columns [*col0, *col0 + *cols) of an N-column result that rank `rank` of `world` computes:
+ * equal blocks rounded up to 32 columns, the last ranks taking what is left. */
+void b200_shard_columns(int64_t N, int world, int rank, int64_t* col0, int64_t* cols);
+
+#define B200_SHARD_FUSED 0 /* tiles are stored into every rank's C by the product kernel itself */
+#define B200_SHARD_NCCL 1  /* local columns, then one ncclAllGather of packed column blocks */
+
+/* C = A x B with B and C split by column blocks over the ranks; every rank passes all of A (M x K),
+ * all of B (K x N; only its own columns are read) and its full-size C, and ends with ALL of C.
+ * Stream-ordered like every other call; collective: all ranks call it with the same shape.
+ *
+ * B200_SHARD_FUSED: [entry barrier] [product kernel] [exit barrier] on `stream`.  The product
+ *   kernel's worker warps store each finished tile into this rank's C and two otherwise idle warps
+ *   copy it from there into every peer's C with plain stores over NVLink while the next tiles are
+ *   multiplied (no multicast, no TMA on peer memory).  C must be the buffer registered as
+ *   c_bufs[rank].  Hazard that the barriers close: a peer's kernel writes into THIS rank's C.  The
+ *   entry barrier holds every rank's stores back until all ranks have reached the call in stream
+ *   order — so work queued earlier on `stream` that still reads the previous result is safe — and the
+ *   exit barrier completes only when every rank's product kernel has finished, so work queued after
+ *   the call sees all columns.  Readers on OTHER streams must be ordered against `stream` by the caller.
+ * B200_SHARD_NCCL: product into a packed staging block, ncclAllGather in place, copies into C.
+ *
+ * A barrier wait that runs out (a peer that never arrives) is bounded at two seconds and reported
+ * by b200_gemm_status as B200_ETIMEDOUT; C is then incomplete. */
+int b200_gemm_f32_sharded(b200_shard_comm* comm, int mode, const float* A, const float* B, float* C,
+                          int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                          int precision, void* stream);
+
+/* The same sharded product from HOST buffers, and nothing is uploaded twice: rank r holds the rows
+ * [r * M / world, (r + 1) * M / world) of A (a_rows, M / world x K), its own columns of B packed
+ * (b_cols, K x cols) and receives its own columns of C packed (c_cols, M x cols, ALL rows), cols as
+ * b200_shard_columns gives them.  Per rank the bus carries 1/world of A, 1/world of B and 1/world
+ * of C.  Pipeline, on four streams: B's columns go up first; A's rows go up in `chunks` pieces
+ * (0 = automatic, at most 16; M / world must divide); each piece is all-gathered over NVLink into
+ * local memory (ncclAllGather, in place) as soon as it has landed; the strip of world * chunk rows
+ * is multiplied as one product as soon as its gather is done; its rows go back to the host while
+ * the next strip is multiplied.  Needs b200_shard_comm_set_nccl when world > 1; M % world == 0.
+ * Returns after the result is on the host; pass page-locked buffers to get the overlap.
+ * Collective: all ranks call it with the same M, N, K and chunks. */
+#define B200_SHARD_MAX_CHUNKS 16
+typedef struct b200_shard_host_layout {
+    int chunks;
+    int64_t rows_per_rank, chunk_rows;
+} b200_shard_host_layout;
+int b200_shard_host_plan(int64_t M, int world, int chunks, b200_shard_host_layout* out);
+int b200_matmul_f32_host_sharded(b200_shard_comm* comm, const float* a_rows, const float* b_cols, float* c_cols,
+                                 int64_t M, int64_t N, int64_t K, int chunks);
 
 /* b200_gemm_f32 for callers that must not allocate device memory.  (No counterpart in the
  * reference: its split-K path always takes its partials from a growable scratch buffer,
@@ -246,8 +349,20 @@ int b200_gemm_f32_static_scratch(const float* A, const float* B, float* C, int64
                                  int* device_status, void* stream);
 
 /* Device-side health of the launches so far on the current device: synchronises the device,
- * returns 0 or B200_ETIMEDOUT if any bounded wait inside a kernel ran out, and clears the flag. */
+ * returns 0 or B200_ETIMEDOUT if any bounded wait inside a kernel ran out, and clears the flag.
+ * Covers the launches of b200_gemm_f32_static_scratch that were given no status pointer too.
+ * (The reference counts failed launches, src/cuda/kernels.cu:81-157; its kernels have no waits.) */
 int b200_gemm_status(void);
+
+/* Test aid for the failure-detection path: launches one warp that waits, with a budget of
+ * budget_us microseconds (1 .. 100000), on a barrier nobody arrives at.  The wait runs out exactly
+ * as a lost copy or a lost tensor-core completion would make a product kernel's wait run out: it
+ * records a status bit and raises the abort flag, and the kernel returns normally — nothing traps
+ * or faults, and the context stays usable.  Synchronises the device.  observed_host (optional,
+ * two ints): [0] = threads whose wait wrongly reported completion (0 expected), [1] = the abort
+ * flag (1 expected).  Afterwards b200_gemm_status() returns B200_ETIMEDOUT once.  Allocates a few
+ * bytes of device memory for the duration of the call. */
+int b200_gemm_selftest_timeout(unsigned budget_us, int* observed_host);
 
 /* Number of kernels this library has launched in this process (all devices). */
 uint64_t b200_gemm_launch_count(void);
@@ -269,7 +384,15 @@ uint64_t b200_gemm_launch_count(void);
  *                   tensor core truncates them itself, which saves a pass over every tile (twice the
  *                   operand error, biased towards zero)
  *   "pair_mode"     0 = automatic, 1 = never, 2 = whenever legal: run 256 x 256 tiles on pairs of
- *                   CTAs (tcgen05 cta_group::2) */
+ *                   CTAs (tcgen05 cta_group::2)
+ *   "head_mode"     3xTF32 with the TMA loader: 0 (default) = the workers round every value to its
+ *                   nearest TF32 head and write head and tail; 1 = the tensor core's own truncation
+ *                   of the raw tile is the head and only the tail is written (one shared-memory
+ *                   store pass less; representation error 2^-21 instead of 2^-22 per operand)
+ *   "pdl"           1 (default) = kernels are launched with programmatic stream serialization: the
+ *                   set-up of a product overlaps the end of the kernel before it; 0 = plain launches
+ *   "map_cache"     1 (default) = encoded TMA tensor maps are reused between calls with the same
+ *                   pointers and shapes, 0 = every call encodes its own */
 int b200_gemm_set_option(const char* name, long value);
 
 /* Static description of a code, never NULL. */

@@ -17,15 +17,26 @@ def check(pkg, orc, cuda, a, b, K, backward=True):
     got = pkg.matmul(dev(a, cuda), dev(b, cuda))
     pkg.status()
     want = orc.matmul(a, b)
-    assert orc.scaled_error(got.cpu().numpy(), want) <= orc.parity_tolerance(K)
+    got = got.cpu().numpy()
+    assert orc.scaled_error(got, want) <= orc.parity_tolerance(K)
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    orc.assert_no_further_from_fp64(got, want, np.matmul(a64, b64))
     if backward:
         g = orc.Rng(99).randn(want.shape)
         dA, dB = pkg.matmul_backward(dev(a, cuda), dev(b, cuda), dev(g, cuda))
         pkg.status()
         wa, wb = orc.matmul_backward(a, b, g)
         kb = max(want.shape[-1], int(np.prod(want.shape[:-1])))
-        assert orc.scaled_error(dA.cpu().numpy(), wa) <= orc.parity_tolerance(want.shape[-1])
-        assert orc.scaled_error(dB.cpu().numpy(), wb) <= orc.parity_tolerance(kb)
+        dA, dB = dA.cpu().numpy(), dB.cpu().numpy()
+        assert orc.scaled_error(dA, wa) <= orc.parity_tolerance(want.shape[-1])
+        assert orc.scaled_error(dB, wb) <= orc.parity_tolerance(kb)
+        g64 = g.astype(np.float64)
+        orc.assert_no_further_from_fp64(dA, wa, np.matmul(g64, np.swapaxes(b64, -1, -2)))
+        if b.ndim == 2 and a.ndim > 2:  # shared weight: its gradient sums over the batch (fold_leading)
+            ref_b = np.matmul(np.swapaxes(a64, -1, -2), g64).sum(axis=tuple(range(a.ndim - 2)))
+            orc.assert_no_further_from_fp64(dB, wb, ref_b)
+        elif a.ndim == b.ndim:
+            orc.assert_no_further_from_fp64(dB, wb, np.matmul(np.swapaxes(a64, -1, -2), g64))
 
 
 def xavier(g, fan_in, fan_out):
@@ -124,47 +135,60 @@ def test_relu_sparse_2048(pkg, orc, cuda, form):
     pkg.status()
     got = C.cpu().numpy()
     assert orc.scaled_error(got, want) <= orc.parity_tolerance(n)
-    # against fp64 the kernel must be no worse than the reference's own fp32 loop
+    # Against fp64 the kernel is far closer than the reference's own fp32 loop (measured 2.6e-5
+    # against 9.7e-5 with a promotion to fp32 registers after every k-block; promoting every 4th
+    # k-block gives 6.3e-5): holding it to half the loop's error is what catches a regression of
+    # the accumulation scheme, which the wide bound above would let through.
     rows = np.arange(0, n, 16)
     ref64 = (opa[rows].astype(np.float64) @ opb.astype(np.float64))
-    assert orc.scaled_error(got[rows], ref64) <= 1.5 * orc.scaled_error(want[rows], ref64) + 1e-6
+    err_gpu, err_cpu = orc.scaled_error(got[rows], ref64), orc.scaled_error(want[rows], ref64)
+    assert err_gpu <= 0.5 * err_cpu, (err_gpu, err_cpu)
 
 
 def test_large_square_properties_4096(pkg, orc, cuda):
-    """4096^3, N(0, 1/K) inputs: sampled rows against the CPU oracle (rows are independent in
-    the reference loop, so those rows are exactly what the full product holds), run-to-run
-    bit-identity, and linearity in alpha."""
+    """4096^3 on the bytes the reference's own generator produces for this configuration
+    (manual_seed(1), then A and B = Tensor::randn({n, n}, 0, 1/sqrt(n)) in that order): sampled rows
+    against the CPU oracle at the flat 1e-5 (rows are independent in the reference loop, so those
+    rows are exactly what the full product holds) and against fp64, run-to-run bit-identity, and
+    linearity in alpha."""
     import torch
 
     n = 4096
-    gen = torch.Generator(device=cuda).manual_seed(1)
-    A = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
-    B = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
+    g = orc.Rng(1)
+    a = g.randn((n, n), 0.0, n ** -0.5)
+    b = g.randn((n, n), 0.0, n ** -0.5)
+    A, B = dev(a, cuda), dev(b, cuda)
+    ws_bytes = pkg.workspace_bytes(1, n, n, n)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=cuda)
     C = torch.empty((n, n), device=cuda)
-    pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n)
+    pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, workspace=ws, workspace_bytes=ws_bytes)
     C2 = torch.empty((n, n), device=cuda)
-    pkg.gemm(A, B, C2, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n)
+    pkg.gemm(A, B, C2, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, workspace=ws, workspace_bytes=ws_bytes)
     pkg.status()
     assert torch.equal(C, C2)
-    rows = torch.arange(5, n, 97, device=cuda)
-    a_rows = A[rows].cpu().numpy()
-    want = orc.matmul(a_rows, B.cpu().numpy())
-    assert orc.scaled_error(C[rows].cpu().numpy(), want) <= 1e-5
-    pkg.gemm(A, B, C2, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, alpha=2.0)
+    rows = np.arange(5, n, 97)
+    got = C.cpu().numpy()[rows]
+    want = orc.matmul(a[rows], b)
+    assert orc.scaled_error(got, want) <= 1e-5
+    ref64 = a[rows].astype(np.float64) @ b.astype(np.float64)
+    err_gpu, err_cpu = orc.scaled_error(got, ref64), orc.scaled_error(want, ref64)
+    assert err_gpu <= 2e-7 and err_gpu <= err_cpu, (err_gpu, err_cpu)
+    pkg.gemm(A, B, C2, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n, alpha=2.0, workspace=ws,
+             workspace_bytes=ws_bytes)
     pkg.status()
     assert torch.equal(C2, 2.0 * C)
 
 
 def test_largest_config_16384(pkg, orc, cuda):
-    """Configuration 5 at its full size, 16384^3 with N(0, 1/K) inputs (3 GiB on the device): sampled rows
+    """Configuration 5 at its full size, 16384^3 with N(0, 1/K) inputs drawn by the reference's generator (3 GiB on the device): sampled rows
     against the CPU loop (rows are independent there, so these are the rows of the full product) and against
     fp64, run-to-run bit-identity, and the plan with the K-split last wave against the plan without it."""
     import torch
 
     n = 16384
-    gen = torch.Generator(device=cuda).manual_seed(1)
-    A = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
-    B = torch.randn((n, n), device=cuda, generator=gen) / n ** 0.5
+    g = orc.Rng(1)  # the reference generator's bytes: manual_seed(1), then A, then B
+    A = dev(g.randn((n, n), 0.0, n ** -0.5), cuda)
+    B = dev(g.randn((n, n), 0.0, n ** -0.5), cuda)
     C = torch.empty((n, n), device=cuda)
     pkg.gemm(A, B, C, batch=1, M=n, N=n, K=n, lda=n, ldb=n, ldc=n)
     pkg.status()
@@ -172,7 +196,9 @@ def test_largest_config_16384(pkg, orc, cuda):
     got = C[rows].cpu().numpy()
     b_host = B.cpu().numpy()
     want = orc.matmul(A[rows].cpu().numpy(), b_host)
-    assert orc.scaled_error(got, want) <= orc.parity_tolerance(n)
+    # N(0, 1/K) inputs keep the outputs of order one and the CPU loop's drift small: the flat 1e-5
+    # of the reference's parity tests holds at K = 16384 too (measured 3e-7)
+    assert orc.scaled_error(got, want) <= 1e-5
     ref64 = (A[rows].double() @ B.double()).cpu().numpy()
     err_gpu, err_cpu = orc.scaled_error(got, ref64), orc.scaled_error(want, ref64)
     assert err_gpu <= 1e-6 and err_gpu <= err_cpu, (err_gpu, err_cpu)

@@ -57,6 +57,7 @@ def test_reference_parity_shapes(pkg, orc, cuda, sa, sb):
     got = run_matmul(pkg, cuda, a, b)
     assert got.shape == want.shape
     assert orc.scaled_error(got, want) <= orc.parity_tolerance(sa[-1])
+    orc.assert_no_further_from_fp64(got, want, np.matmul(a.astype(np.float64), b.astype(np.float64)))
 
 
 @pytest.mark.parametrize("sa,sb", REFERENCE_SHAPES)
@@ -78,7 +79,10 @@ def test_split_k_shapes(pkg, orc, cuda, M, K, N):
     a, b = g.randn((M, K)), g.randn((K, N))
     assert pkg.workspace_bytes(1, M, N, K) > 0, "expected the split-K path for this shape"
     got = run_matmul(pkg, cuda, a, b)
-    assert orc.scaled_error(got, orc.matmul(a, b)) <= orc.parity_tolerance(K)
+    want = orc.matmul(a, b)
+    assert orc.scaled_error(got, want) <= orc.parity_tolerance(K)
+    # the wide bound is for the CPU loop's drift over a long K; the kernel itself is held to fp64
+    orc.assert_no_further_from_fp64(got, want, a.astype(np.float64) @ b.astype(np.float64))
     rng = np.random.default_rng(3)
     ai = rng.integers(-2, 3, size=(M, K)).astype(np.float32)
     bi = rng.integers(-2, 3, size=(K, N)).astype(np.float32)
@@ -143,6 +147,7 @@ def test_transposed_forms_match_materialised_transposes(pkg, orc, cuda, form, M,
     gemm(pkg, cuda, dev(a, cuda), dev(b, cuda), C, batch=1, M=M, N=N, K=K, transA=tA, transB=tB,
          lda=a.shape[1], ldb=b.shape[1], ldc=N)
     assert orc.scaled_error(C.cpu().numpy(), want) <= orc.parity_tolerance(K)
+    orc.assert_no_further_from_fp64(C.cpu().numpy(), want, opa.astype(np.float64) @ opb.astype(np.float64))
 
 
 def test_sentinel_padding_stays_untouched(pkg, orc, cuda):
