@@ -27,9 +27,10 @@
  * Finite inputs only.  The reference's CPU loop skips every term whose A value is exactly zero
  * (src/tensor_ops.cpp:555), so it never forms 0 * Inf or 0 * NaN; for finite inputs the skip
  * changes nothing, and zeros in A give the same results here as there.  An infinite or NaN input,
- * however, turns the affected outputs into NaN here (the split forms Inf - Inf), where the
- * reference yields +-Inf or leaves rows with a zero A value untouched.  Callers that may hold
- * non-finite values must clean them first.
+ * however, makes every output that its row or column feeds non-finite here — NaN where the
+ * reference may hold +-Inf (the split forms Inf - Inf), and also where the reference skipped the
+ * term because the A value was zero and kept a finite result.  Outputs that the value does not
+ * feed are unaffected.  Callers that may hold non-finite values must clean them first.
  *
  * Threads.  Like the reference's device layer (one dispatching thread, src/cuda/runtime.cu:159-160)
  * the library expects one thread per device to issue products.  Calls from several threads are

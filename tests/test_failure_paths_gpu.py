@@ -61,8 +61,9 @@ def test_zeros_in_a_behave_like_the_reference_skip_for_finite_inputs(pkg, orc, c
 
 def test_non_finite_inputs_differ_from_the_reference_as_documented(pkg, orc, cuda):
     """include/b200_gemm.h: finite inputs only.  An infinite B value met by a zero A value is
-    skipped by the reference (the row stays finite) and becomes NaN here; rows that do not touch
-    the non-finite value are unaffected."""
+    skipped by the reference (that output stays finite) and is not finite here; the other outputs of
+    the column are +-inf there and NaN or +-inf here; columns that do not touch the value are
+    unaffected."""
     g = orc.Rng(7)
     a, b = g.randn((64, 40)), g.randn((40, 48))
     a[0, 5] = 0.0
@@ -73,6 +74,7 @@ def test_non_finite_inputs_differ_from_the_reference_as_documented(pkg, orc, cud
     got = pkg.matmul(dev(a, cuda), dev(b, cuda))
     pkg.status()
     got = got.cpu().numpy()
-    assert np.isnan(got[:, 9]).all()             # documented: NaN, not +-inf or the skipped value
+    assert not np.isfinite(got[:, 9]).any()      # documented: NaN or +-inf, the skipped term included
+    assert np.isnan(got[0, 9])                   # 0 * inf was formed
     cols = np.arange(48) != 9
     assert orc.scaled_error(got[:, cols], want[:, cols]) <= 1e-5
