@@ -14,6 +14,9 @@ from __future__ import annotations
 from . import build as _build  # noqa: F401
 from .lib import (  # noqa: F401
     B200Error,
+    attention_any,
+    attention_any_workspace,
+    attention_backward_any,
     attention_forward,
     conv2d_forward,
     PRECISION_3XTF32,

@@ -9,7 +9,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB = PKG_DIR / "libb200gemm.so"
-SOURCES = [CSRC / "gemm_sm100.cu", CSRC / "shard_sm100.cu"]
+SOURCES = [CSRC / "gemm_sm100.cu", CSRC / "shard_sm100.cu", CSRC / "attention_any.cu"]
 HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "attention_kernel.cuh", CSRC / "attention_bwd_kernel.cuh", CSRC / "sm100_ptx.cuh", CSRC / "shard_layout.h", PKG_DIR.parent / "include" / "b200_gemm.h"]
 
 NVCC_FLAGS = [

@@ -597,7 +597,11 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll || batch > 0x7fffffffll)
         return B200_ERANGE;
     if (ldc < N || strideC < 0 || strideA < 0 || strideB < 0) return B200_EINVAL;
-    if (batch > 1 && strideC < M * ldc && strideC != 0) return B200_EINVAL;
+    if (batch > 1 && strideC < M * ldc && strideC != 0) {
+        // matrices closer together than their own extent overlap — unless they sit side by side in the
+        // rows of one buffer (the heads of a (S, heads * d) tensor: strideC >= N and batch * strideC <= ldc)
+        if (!(strideC >= N && batch * strideC <= ldc)) return B200_EINVAL;
+    }
     if (batch > 1 && strideC == 0) return B200_EINVAL;  // every batch would write the same C
     float* C = dest[0];
     if (K == 0) {
@@ -1359,6 +1363,20 @@ uint32_t attention_bwd_layout(b200::AttnBwdParams& p) {
     return total <= 227u * 1024u ? total : 0u;
 }
 }  // namespace
+
+namespace b200 {
+// For the any-size attention layer (attention_any.cu): does the fused backward kernel take this head?
+bool attention_backward_fits_one_cta(int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v) {
+    if (s_q <= 0 || s_k <= 0 || d_k <= 0 || d_v <= 0) return false;
+    if (s_q > 128 || s_k > kAttnMaxSk || d_k > kAttnMaxD || d_v > kAttnMaxD) return false;
+    AttnBwdParams p{};
+    p.s_q = static_cast<int>(s_q);
+    p.s_k = static_cast<int>(s_k);
+    p.d_k = static_cast<int>(d_k);
+    p.d_v = static_cast<int>(d_v);
+    return attention_bwd_layout(p) != 0;
+}
+}  // namespace b200
 
 extern "C" {
 

@@ -198,6 +198,18 @@ def attention_scores(q, k, scale: float, mask=None, *, precision: int = _lib.PRE
     return out
 
 
+def _attention_workspace(device, *, batch, heads, s_q, s_k, d_k, d_v, backward, have_weights=False):
+    """Scratch for heads the fused attention kernels do not take (0 bytes when they do; the forward
+    uses the caller's weights buffer when there is one)."""
+    import torch
+
+    nbytes = _lib.attention_any_workspace(batch=batch, heads=heads, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
+                                          backward=backward)
+    if nbytes == 0 or (have_weights and not backward):
+        return None, 0
+    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
+
+
 def scaled_dot_product_attention(query, key, value, mask=None, *, return_weights: bool = False,
                                  precision: int = _lib.PRECISION_3XTF32, stream=None):
     """``scaled_dot_product_attention`` (src/transformer.cpp:279-304): softmax(Q K^T / sqrt(d_k) + mask) V
@@ -228,8 +240,13 @@ def scaled_dot_product_attention(query, key, value, mask=None, *, return_weights
     out = torch.empty(lead + [s_q, d_v], dtype=torch.float32, device=query.device)
     weights = torch.empty(lead + [s_q, s_k], dtype=torch.float32, device=query.device) if return_weights else None
     if batch:
-        _lib.attention_forward(query, key, value, mask, out, weights, batch=batch, s_q=s_q, s_k=s_k, d_k=d_k,
-                               d_v=d_v, scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+        ws, ws_bytes = _attention_workspace(query.device, batch=batch, heads=1, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
+                                            backward=False, have_weights=weights is not None)
+        _lib.attention_any(query, key, value, mask, out, weights, batch=batch, heads=1, s_q=s_q, s_k=s_k, d_k=d_k,
+                           d_v=d_v, q_strides=(s_q * d_k, 0, d_k), k_strides=(s_k * d_k, 0, d_k),
+                           v_strides=(s_k * d_v, 0, d_v), out_strides=(s_q * d_v, 0, d_v),
+                           scale=1.0 / math.sqrt(float(d_k)), precision=precision, workspace=ws,
+                           workspace_bytes=ws_bytes, stream=stream)
     return (out, weights) if return_weights else out
 
 
@@ -237,8 +254,9 @@ def scaled_dot_product_attention_backward(query, key, value, grad_out, mask=None
                                           precision: int = _lib.PRECISION_3XTF32, stream=None):
     """The gradients autograd hands query, key and value of ``scaled_dot_product_attention`` for ``grad_out``
     (the backward of the five nodes of src/transformer.cpp:279-304), as ONE kernel that recomputes the
-    attention weights: ``(grad_query, grad_key, grad_value)``.  Raises ``RuntimeError`` (B200_ERANGE) for
-    shapes whose tiles do not fit one CTA — S = 64 with head widths up to 64 do."""
+    attention weights: ``(grad_query, grad_key, grad_value)``.  Heads whose tiles do not fit one CTA
+    (S = 64 with head widths up to 64 do) run composed on the device: four batched products through the
+    transposed forms and one row kernel for the softmax backward."""
     import math
 
     import torch
@@ -265,10 +283,13 @@ def scaled_dot_product_attention_backward(query, key, value, grad_out, mask=None
         batch *= d
     gq, gk, gv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
     if batch:
-        _lib.attention_backward_strided(
+        ws, ws_bytes = _attention_workspace(query.device, batch=batch, heads=1, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
+                                            backward=True)
+        _lib.attention_backward_any(
             query, key, value, mask, grad_out, gq, gk, gv, batch=batch, heads=1, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
             q_strides=(s_q * d_k, 0, d_k), k_strides=(s_k * d_k, 0, d_k), v_strides=(s_k * d_v, 0, d_v),
-            out_strides=(s_q * d_v, 0, d_v), scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+            out_strides=(s_q * d_v, 0, d_v), scale=1.0 / math.sqrt(float(d_k)), precision=precision, workspace=ws,
+            workspace_bytes=ws_bytes, stream=stream)
     return gq, gk, gv
 
 
@@ -298,12 +319,14 @@ def multi_head_attention_core_backward(query, key, value, grad_merged, num_heads
     gq, gk, gv = (torch.empty_strided(t.shape, t.stride(), dtype=torch.float32, device=t.device)
                   for t in (query, key, value))
     if batch:
-        _lib.attention_backward_strided(
+        ws, ws_bytes = _attention_workspace(query.device, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k,
+                                            d_v=d_v, backward=True)
+        _lib.attention_backward_any(
             query, key, value, mask, grad_merged, gq, gk, gv, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k,
             d_v=d_v, q_strides=(query.stride(0), d_k, query.stride(1)), k_strides=(key.stride(0), d_k, key.stride(1)),
             v_strides=(value.stride(0), d_v, value.stride(1)),
             out_strides=(grad_merged.stride(0), d_v, grad_merged.stride(1)), scale=1.0 / math.sqrt(float(d_k)),
-            precision=precision, stream=stream)
+            precision=precision, workspace=ws, workspace_bytes=ws_bytes, stream=stream)
     return gq, gk, gv
 
 
@@ -346,11 +369,14 @@ def multi_head_attention_core(query, key, value, num_heads: int, mask=None, *, r
     weights = (torch.empty((batch, num_heads, s_q, s_k), dtype=torch.float32, device=query.device)
                if return_weights else None)
     if batch:
-        _lib.attention_forward_strided(
+        ws, ws_bytes = _attention_workspace(query.device, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k,
+                                            d_v=d_v, backward=False, have_weights=weights is not None)
+        _lib.attention_any(
             query, key, value, mask, out, weights, batch=batch, heads=num_heads, s_q=s_q, s_k=s_k, d_k=d_k, d_v=d_v,
             q_strides=(query.stride(0), d_k, query.stride(1)), k_strides=(key.stride(0), d_k, key.stride(1)),
             v_strides=(value.stride(0), d_v, value.stride(1)), out_strides=(out.stride(0), d_v, out.stride(1)),
-            scale=1.0 / math.sqrt(float(d_k)), precision=precision, stream=stream)
+            scale=1.0 / math.sqrt(float(d_k)), precision=precision, workspace=ws, workspace_bytes=ws_bytes,
+            stream=stream)
     return (out, weights) if return_weights else out
 
 

@@ -817,11 +817,15 @@ void attach_attention_backward(Tensor& out, const Tensor& q, const Tensor& k, co
         }
         auto run = [&](float* const o[3], float beta) {
             if (o[0] == nullptr && o[1] == nullptr && o[2] == nullptr) return;
-            check_b200(b200_attention_backward_f32_strided(
+            // heads the fused kernel does not take run composed on the device and want scratch
+            const size_t ws_bytes = b200_attention_any_workspace(i64(batch), i64(heads), i64(s_q), i64(s_k),
+                                                                 i64(d_k), i64(d_v), 1);
+            void* ws = ws_bytes ? g_scratch.get(ws_bytes) : nullptr;
+            check_b200(b200_attention_backward_any_f32(
                            qi->storage.device(), ki->storage.device(), vi->storage.device(),
                            mi ? mi->storage.device() : nullptr, impl_of(g)->storage.device(), o[0], o[1], o[2],
                            i64(batch), i64(heads), i64(s_q), i64(s_k), i64(d_k), i64(d_v), st.q, st.k, st.v, st.o,
-                           scale, beta, current_precision(), nullptr),
+                           scale, beta, current_precision(), ws, ws_bytes, nullptr),
                        "attention backward");
         };
         run(fresh, 0.0f);
@@ -870,16 +874,22 @@ Tensor scaled_dot_product_attention(const Tensor& query_, const Tensor& key_, co
     if (batch == 0) return out;
     const float scale = 1.0f / std::sqrt(static_cast<float>(d_k));
     const auto i64 = [](size_t x) { return static_cast<int64_t>(x); };
-    check_b200(b200_attention_f32(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
-                                  impl_of(v)->storage.device(), pm, impl_of(out)->storage.device_write(),
-                                  attention_weights ? impl_of(weights)->storage.device_write() : nullptr,
-                                  i64(batch), i64(s_q), i64(s_k), i64(d_k), i64(d_v), scale, current_precision(),
-                                  nullptr),
-               "scaled_dot_product_attention");
+    const int64_t qs[3] = {i64(s_q * d_k), 0, i64(d_k)}, ks[3] = {i64(s_k * d_k), 0, i64(d_k)};
+    const int64_t vs[3] = {i64(s_k * d_v), 0, i64(d_v)}, os[3] = {i64(s_q * d_v), 0, i64(d_v)};
+    {
+        const size_t ws_bytes = attention_weights ? 0
+                                                  : b200_attention_any_workspace(i64(batch), 1, i64(s_q), i64(s_k),
+                                                                                 i64(d_k), i64(d_v), 0);
+        void* ws = ws_bytes ? g_scratch.get(ws_bytes) : nullptr;
+        check_b200(b200_attention_any_f32(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
+                                          impl_of(v)->storage.device(), pm, impl_of(out)->storage.device_write(),
+                                          attention_weights ? impl_of(weights)->storage.device_write() : nullptr,
+                                          i64(batch), 1, i64(s_q), i64(s_k), i64(d_k), i64(d_v), qs, ks, vs, os, scale,
+                                          current_precision(), ws, ws_bytes, nullptr),
+                   "scaled_dot_product_attention");
+    }
     if (attention_weights) *attention_weights = weights;
     if (tracked) {
-        const int64_t qs[3] = {i64(s_q * d_k), 0, i64(d_k)}, ks[3] = {i64(s_k * d_k), 0, i64(d_k)};
-        const int64_t vs[3] = {i64(s_k * d_v), 0, i64(d_v)}, os[3] = {i64(s_q * d_v), 0, i64(d_v)};
         attach_attention_backward(out, q, k, v, mask_keep, mask != nullptr, batch, 1, s_q, s_k, d_k, d_v, qs, ks, vs,
                                   os, scale);
     }
@@ -916,11 +926,16 @@ Tensor multi_head_attention_core(const Tensor& query_, const Tensor& key_, const
     const int64_t vs[3] = {i64(s_k * dv_model), i64(d_v), i64(dv_model)};
     const int64_t os[3] = {i64(s_q * dv_model), i64(d_v), i64(dv_model)};
     const float scale = 1.0f / std::sqrt(static_cast<float>(d_k));
-    check_b200(b200_attention_f32_strided(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
+    {
+        const size_t ws_bytes = b200_attention_any_workspace(i64(batch), i64(num_heads), i64(s_q), i64(s_k), i64(d_k),
+                                                             i64(d_v), 0);
+        void* ws = ws_bytes ? g_scratch.get(ws_bytes) : nullptr;
+        check_b200(b200_attention_any_f32(impl_of(q)->storage.device(), impl_of(k)->storage.device(),
                                           impl_of(v)->storage.device(), pm, impl_of(out)->storage.device_write(),
-                                          nullptr, i64(batch), i64(num_heads), i64(s_q), i64(s_k), i64(d_k),
-                                          i64(d_v), qs, ks, vs, os, scale, current_precision(), nullptr),
-               "multi_head_attention_core");
+                                          nullptr, i64(batch), i64(num_heads), i64(s_q), i64(s_k), i64(d_k), i64(d_v),
+                                          qs, ks, vs, os, scale, current_precision(), ws, ws_bytes, nullptr),
+                   "multi_head_attention_core");
+    }
     if (tracked) {
         attach_attention_backward(out, q, k, v, mask_keep, mask != nullptr, batch, num_heads, s_q, s_k, d_k, d_v, qs,
                                   ks, vs, os, scale);

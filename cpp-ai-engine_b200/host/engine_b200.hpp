@@ -200,10 +200,11 @@ Tensor conv2d(const Tensor& input, const Tensor& weight, const Tensor* bias, con
 
 // scaled_dot_product_attention over the leading (batch, head) axes: softmax(Q K^T / sqrt(d_k) +
 // mask) V in one kernel; attention_weights, if given, receives the softmax output.  Gradients flow
-// to query, key and value through ONE backward kernel that recomputes the weights.  Limits: S_q,
-// S_k <= 128 and d_k, d_v <= 64 (std::runtime_error beyond); the backward also needs the tiles of
-// a head to fit one CTA (S = 64 with d <= 64 does, S = 128 does not: std::runtime_error from
-// backward() — train such shapes through the separate products).
+// to query, key and value through ONE backward kernel that recomputes the weights.  Any size, like
+// the reference's: heads beyond the fused kernels' tiles (S_q, S_k <= 128 and d_k, d_v <= 64 forward;
+// the tiles of a head in one CTA's shared memory backward — S = 64 with d <= 64 fits, S = 128 does
+// not) run composed on the device (b200_attention_any_f32: products with the scale and the mask in
+// their store, owned softmax row kernels), never on the host.
 Tensor scaled_dot_product_attention(const Tensor& query, const Tensor& key, const Tensor& value,
                                     const Tensor* mask = nullptr, Tensor* attention_weights = nullptr);
 

@@ -24,6 +24,9 @@ EXPORTS = (
     "b200_attention_f32_strided",
     "b200_attention_backward_f32",
     "b200_attention_backward_f32_strided",
+    "b200_attention_any_workspace",
+    "b200_attention_any_f32",
+    "b200_attention_backward_any_f32",
     "b200_conv2d_forward_f32",
     "b200_conv2d_backward_workspace",
     "b200_conv2d_backward_f32",
@@ -108,6 +111,14 @@ def load() -> ctypes.CDLL:
     lib.b200_attention_backward_f32_strided.restype = c_int
     lib.b200_attention_backward_f32_strided.argtypes = ([c_vp] * 8 + [c_i64] * 6 + [ctypes.POINTER(c_i64)] * 4
                                                         + [c_f, c_f, c_int, c_vp])
+    lib.b200_attention_any_workspace.restype = c_sz
+    lib.b200_attention_any_workspace.argtypes = [c_i64] * 6 + [c_int]
+    lib.b200_attention_any_f32.restype = c_int
+    lib.b200_attention_any_f32.argtypes = ([c_vp] * 6 + [c_i64] * 6 + [ctypes.POINTER(c_i64)] * 4
+                                           + [c_f, c_int, c_vp, c_sz, c_vp])
+    lib.b200_attention_backward_any_f32.restype = c_int
+    lib.b200_attention_backward_any_f32.argtypes = ([c_vp] * 8 + [c_i64] * 6 + [ctypes.POINTER(c_i64)] * 4
+                                                    + [c_f, c_f, c_int, c_vp, c_sz, c_vp])
     lib.b200_conv2d_forward_f32.restype = c_int
     lib.b200_conv2d_forward_f32.argtypes = [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 9 + [c_int, c_int, c_vp]
     lib.b200_conv2d_backward_workspace.restype = c_sz
@@ -255,6 +266,37 @@ def attention_backward_strided(q, k, v, mask, dout, dq, dk, dv, *, batch: int, h
         d_v, arr(*q_strides), arr(*k_strides), arr(*v_strides), arr(*out_strides), scale, beta, precision,
         _stream_ptr(stream))
     _check(rc, "b200_attention_backward_f32_strided")
+
+
+def attention_any_workspace(*, batch: int, heads: int, s_q: int, s_k: int, d_k: int, d_v: int,
+                            backward: bool = False) -> int:
+    """Bytes of workspace ``attention_any`` / ``attention_backward_any`` want for this shape (0: fused kernel)."""
+    return int(load().b200_attention_any_workspace(batch, heads, s_q, s_k, d_k, d_v, int(backward)))
+
+
+def attention_any(q, k, v, mask, out, weights, *, batch: int, heads: int, s_q: int, s_k: int, d_k: int, d_v: int,
+                  q_strides, k_strides, v_strides, out_strides, scale: float, precision: int = PRECISION_3XTF32,
+                  workspace=None, workspace_bytes: int = 0, stream=None) -> None:
+    """Attention for heads of any size: the fused kernel when the head fits it, else composed on the device."""
+    arr = ctypes.c_int64 * 3
+    rc = load().b200_attention_any_f32(_ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(out), _ptr(weights), batch, heads,
+                                       s_q, s_k, d_k, d_v, arr(*q_strides), arr(*k_strides), arr(*v_strides),
+                                       arr(*out_strides), scale, precision, _ptr(workspace), workspace_bytes,
+                                       _stream_ptr(stream))
+    _check(rc, "b200_attention_any_f32")
+
+
+def attention_backward_any(q, k, v, mask, dout, dq, dk, dv, *, batch: int, heads: int, s_q: int, s_k: int, d_k: int,
+                           d_v: int, q_strides, k_strides, v_strides, out_strides, scale: float, beta: float = 0.0,
+                           precision: int = PRECISION_3XTF32, workspace=None, workspace_bytes: int = 0,
+                           stream=None) -> None:
+    """Gradients of :func:`attention_any`, any size."""
+    arr = ctypes.c_int64 * 3
+    rc = load().b200_attention_backward_any_f32(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dout), _ptr(dq), _ptr(dk), _ptr(dv), batch, heads, s_q, s_k, d_k,
+        d_v, arr(*q_strides), arr(*k_strides), arr(*v_strides), arr(*out_strides), scale, beta, precision,
+        _ptr(workspace), workspace_bytes, _stream_ptr(stream))
+    _check(rc, "b200_attention_backward_any_f32")
 
 
 def conv2d_backward_workspace(*, n: int, c: int, h: int, w: int, out_c: int, kh: int, kw: int, stride: int = 1,

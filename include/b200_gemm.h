@@ -148,7 +148,7 @@ int b200_conv2d_backward_f32(const float* x, const float* weight, const float* d
  * columns in ascending order, divide).  q: (batch, s_q, d_k); k: (batch, s_k, d_k); v: (batch, s_k, d_v); mask: (s_q, s_k)
  * additive and shared by every batch element, or NULL; out: (batch, s_q, d_v); weights: optional
  * (batch, s_q, s_k) copy of the softmax output (the reference's attention_weights), or NULL.
- * Limits: s_q <= 128, s_k <= 128, d_k <= 64, d_v <= 64 (B200_ERANGE beyond; use the separate products). */
+ * Limits: s_q <= 128, s_k <= 128, d_k <= 64, d_v <= 64 (B200_ERANGE beyond; b200_attention_any_f32 takes every size). */
 int b200_attention_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
                        float* weights, int64_t batch, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
                        float scale, int precision, void* stream);
@@ -179,7 +179,8 @@ int b200_attention_f32_strided(const float* q, const float* k, const float* v, c
  * global memory.  dq, dk, dv (any may be NULL) are addressed like q, k, v; dout like the forward's
  * out; beta = 0 overwrites, beta = 1 accumulates (Tensor::add_grad, src/tensor.cpp:168-203).
  * Limits: those of the forward kernel AND the tiles of a head must fit one CTA's shared memory
- * (S = 64 with d <= 64 does; S = 128 does not): B200_ERANGE otherwise — use the separate products. */
+ * (S = 64 with d <= 64 does; S = 128 does not): B200_ERANGE otherwise — b200_attention_backward_any_f32
+ * takes every size. */
 int b200_attention_backward_f32(const float* q, const float* k, const float* v, const float* mask,
                                 const float* dout, float* dq, float* dk, float* dv, int64_t batch,
                                 int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v, float scale, float beta,
@@ -190,6 +191,33 @@ int b200_attention_backward_f32_strided(const float* q, const float* k, const fl
                                         const int64_t q_strides[3], const int64_t k_strides[3],
                                         const int64_t v_strides[3], const int64_t out_strides[3],
                                         float scale, float beta, int precision, void* stream);
+
+/* scaled_dot_product_attention and its backward for heads of ANY size (the reference's take any S and d,
+ * src/transformer.cpp:279-304).  Same arguments as the _strided forms plus a workspace.  Heads that fit the
+ * fused kernels run there and need no workspace.  Every other shape runs composed on the device, as the
+ * reference composes it but without its transposes and separate element-wise passes: the scores as one
+ * batched product on k as stored with `* scale` and `+ mask` in its store, an owned row-softmax kernel in
+ * the reference's order (maximum, exp, sum, divide: src/tensor_ops.cpp:621-647), weights x v; for the
+ * gradients the weights again, dW = dout x v^T, dv = W^T x dout, the softmax backward
+ * dS = W o (dW - rowsum(dW o W)) * scale as one row kernel (src/tensor_ops.cpp:649-668), dq = dS x k,
+ * dk = dS^T x q.  When (batch, heads) fold into one stride the products are single launches over
+ * batch * heads matrices, otherwise one launch per batch element over its heads.
+ * workspace: b200_attention_any_workspace() bytes (0 when the fused kernel takes the shape), 16-byte
+ * aligned; too little is B200_ENOSPACE.  The forward uses `weights`, when given, instead of workspace. */
+size_t b200_attention_any_workspace(int64_t batch, int64_t heads, int64_t s_q, int64_t s_k, int64_t d_k,
+                                    int64_t d_v, int backward);
+int b200_attention_any_f32(const float* q, const float* k, const float* v, const float* mask, float* out,
+                           float* weights, int64_t batch, int64_t heads, int64_t s_q, int64_t s_k, int64_t d_k,
+                           int64_t d_v, const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t out_strides[3], float scale, int precision,
+                           void* workspace, size_t workspace_bytes, void* stream);
+int b200_attention_backward_any_f32(const float* q, const float* k, const float* v, const float* mask,
+                                    const float* dout, float* dq, float* dk, float* dv, int64_t batch,
+                                    int64_t heads, int64_t s_q, int64_t s_k, int64_t d_k, int64_t d_v,
+                                    const int64_t q_strides[3], const int64_t k_strides[3],
+                                    const int64_t v_strides[3], const int64_t out_strides[3], float scale,
+                                    float beta, int precision, void* workspace, size_t workspace_bytes,
+                                    void* stream);
 
 /* Bytes of workspace with which b200_gemm_f32 can use split-K for this shape (0 when it would
  * not split).  Replaces the reference's scratch_buffer for its split-K partials

@@ -125,8 +125,12 @@ def test_limits_are_refused_not_faked(pkg, cuda):
     import torch
 
     big = torch.zeros((2, 128, 64), device=cuda)
-    with pytest.raises(RuntimeError):       # the tiles of S = 128, d = 64 do not fit one CTA
-        pkg.scaled_dot_product_attention_backward(big, big, big, big)
+    with pytest.raises(pkg.B200Error) as err:  # the tiles of S = 128, d = 64 do not fit one CTA: the fused
+        pkg.lib.attention_backward_strided(     # kernel's own entry point says so
+            big, big, big, None, big, big.clone(), big.clone(), big.clone(), batch=2, heads=1, s_q=128, s_k=128,
+            d_k=64, d_v=64, q_strides=(8192, 0, 64), k_strides=(8192, 0, 64), v_strides=(8192, 0, 64),
+            out_strides=(8192, 0, 64), scale=0.125)
+    assert err.value.code == -2
     with pytest.raises(ValueError):
         pkg.scaled_dot_product_attention_backward(big, big, big, torch.zeros((2, 128, 32), device=cuda))
 

@@ -74,9 +74,15 @@ def test_limits_are_reported_not_silently_wrong(pkg, cuda):
     import torch
 
     q = torch.zeros((2, 129, 8), device=cuda)
-    with pytest.raises(pkg.B200Error) as err:
-        pkg.scaled_dot_product_attention(q, q, q)
+    out = torch.empty((2, 129, 8), device=cuda)
+    with pytest.raises(pkg.B200Error) as err:  # the fused kernel's own entry point keeps its limits
+        pkg.lib.attention_forward(q, q, q, None, out, None, batch=2, s_q=129, s_k=129, d_k=8, d_v=8, scale=1.0)
     assert err.value.code == -2
+    with pytest.raises(pkg.B200Error) as err:  # the any-size entry point without the scratch it asks for
+        pkg.attention_any(q, q, q, None, out, None, batch=2, heads=1, s_q=129, s_k=129, d_k=8, d_v=8,
+                          q_strides=(129 * 8, 0, 8), k_strides=(129 * 8, 0, 8), v_strides=(129 * 8, 0, 8),
+                          out_strides=(129 * 8, 0, 8), scale=1.0)
+    assert err.value.code == -3
     with pytest.raises(ValueError):
         pkg.scaled_dot_product_attention(torch.zeros((2, 4, 8), device=cuda), torch.zeros((2, 4, 6), device=cuda),
                                          torch.zeros((2, 4, 6), device=cuda))
