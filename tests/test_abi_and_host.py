@@ -255,3 +255,11 @@ def test_sharded_host_layout_two_ranks_gloo():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_integration_doc_shows_the_seam_unit_that_is_compiled():
+    """INTEGRATION.md prints oracle/seam/matmul_b200.cpp verbatim: the binding a maintainer is shown is
+    the file `make -C oracle ref_cuda` compiles against the unmodified reference."""
+    doc = (ROOT / "INTEGRATION.md").read_text()
+    unit = (ROOT / "oracle" / "seam" / "matmul_b200.cpp").read_text()
+    assert unit in doc

@@ -71,7 +71,11 @@ def _rank_main(rank, world, port, mode, M, N, K, results):
                 h_c.fill_(float("nan"))
                 hop(h_a.numpy(), h_b.numpy(), h_c.numpy())
             pkg.status()
-            ok["own_columns_bit_equal_to_one_gpu"] = bool(torch.equal(h_c, whole[:, col0:col0 + cols].cpu()))
+            # A strip is a product of its own (fewer rows): the planner may split its K where the whole
+            # product's is not split, so the columns agree to rounding, not bit for bit; a misplaced row or
+            # chunk would be off by the size of the values.
+            ok["own_columns_match_one_gpu"] = bool(
+                orc.scaled_error(h_c.numpy(), whole[:, col0:col0 + cols].cpu().numpy()) <= 2e-6)
             rows = np.arange(1, M, 53)
             ok["parity_vs_cpu_oracle"] = bool(
                 orc.scaled_error(h_c.numpy()[rows], orc.matmul(a[rows], np.ascontiguousarray(b[:, col0:col0 + cols])))
