@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--no-peak", action="store_true", help="skip the cuBLAS TF32 context measurement (profiling runs)")
     ap.add_argument("--warm-seconds", type=float, default=2.0,
                     help="minimum duration of the untimed warm-up loop (same power state at every N)")
+    ap.add_argument("--max-windows", type=int, default=50,
+                    help="upper bound on the timed windows of --steps steps (1 for profiling runs)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="library option (b200_gemm_set_option), e.g. --opt pdl=0; repeatable")
     ap.add_argument("--suite", default="", choices=["", "engine", "accuracy"],
@@ -74,8 +76,11 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
+    def __init__(self, gpu):
+        """`gpu`: what `nvidia-smi -i` takes — an index or, better, the GPU's UUID (an index means the
+        physical GPU of that number, which is not the CUDA device of that number once
+        CUDA_VISIBLE_DEVICES remaps them)."""
+        self.gpu = gpu
         self.proc = None
 
     def start(self):
@@ -117,6 +122,43 @@ class ClockSampler:
             return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
                     "samples": len(sm), "power_w_max": max(power) if power else None}
         return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+
+
+def gpu_identity(torch, local: int):
+    """(`nvidia-smi -i` selector, PCI bus id) of CUDA device `local`."""
+    props = torch.cuda.get_device_properties(local)
+    uuid = getattr(props, "uuid", None)
+    sel = f"GPU-{uuid}" if uuid is not None and not str(uuid).startswith("GPU-") else (str(uuid) if uuid else str(local))
+    try:
+        bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    except AttributeError:
+        bus = None
+    return sel, bus
+
+
+def bind_host_thread_near_gpu(bus_id):
+    """Runs this process on the CPU cores NVML lists as local to the GPU, so that the page-locked host
+    buffers it allocates next sit in that socket's memory (first touch) and uploads do not cross the
+    socket link.  Returns the previous affinity mask (to restore), or None when nothing was changed.
+    Only this process's CPU affinity is touched; nothing of the GPU is."""
+    if not bus_id or not hasattr(os, "sched_setaffinity"):
+        return None
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {w * 64 + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        before = os.sched_getaffinity(0)
+        cpus &= before
+        if not cpus or cpus == before:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return before
+    except Exception:
+        return None
 
 
 # ------------------------------------------------------------------------------------------
@@ -354,7 +396,8 @@ def run_b200(args):
         return max_over_ranks(e0.elapsed_time(e1))
 
     # Every rank samples its own GPU's clocks from here to the end of the timed windows.
-    sampler = ClockSampler(local)
+    gpu_sel, gpu_bus = gpu_identity(torch, local)
+    sampler = ClockSampler(gpu_sel)
     sampler.start()
     # Warm-up: the requested count (at least 3) AND at least two seconds of back-to-back steps, at
     # every N, so that every GPU is in the same power state (power-capped, clocks settled) when the
@@ -364,7 +407,7 @@ def run_b200(args):
     barrier()
     t_warm = time.perf_counter()
     warm_steps = max(3, args.warmup)
-    while True:
+    while args.warm_seconds > 0:
         for _ in range(4):
             step()
         warm_steps += 4
@@ -377,7 +420,7 @@ def run_b200(args):
     # the line reports the median window.
     launches0 = pkg.launch_count()
     windows = [timed_window(step, args.steps)]
-    while sum(windows) < 1000.0 and len(windows) < 50:
+    while sum(windows) < 1000.0 and len(windows) < args.max_windows:
         windows.append(timed_window(step, args.steps))
     launches = (pkg.launch_count() - launches0) // len(windows)
     clocks_mine = sampler.stop()
@@ -530,6 +573,7 @@ def run_b200(args):
     e2e = None
     if not args.no_extras:
         reps = max(2, min(args.steps, 4))
+        old_affinity = bind_host_thread_near_gpu(gpu_bus)  # pinned buffers in the GPU's own socket
         if world == 1:
             h_a = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
             h_b = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
@@ -584,8 +628,11 @@ def run_b200(args):
             ref = A[rr].double() @ B[:, col0:col0 + cols].double()
         e2e_err = max_over_ranks(float(((got.double() - ref).abs() / ref.abs().clamp(min=1.0)).max().item())
                                  if got.numel() else 0.0)
+        if old_affinity is not None:
+            os.sched_setaffinity(0, old_affinity)  # the CPU leg below uses every host thread again
         e2e = {"value": flops / secs / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": secs * 1e3, "path": path,
+               "host_buffers_bound_to_gpu_socket": old_affinity is not None,
                "scaled_max_error_vs_fp64_sampled_rows": e2e_err}
     if rank == 0:
         line["e2e"] = e2e

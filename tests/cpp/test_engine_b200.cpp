@@ -386,6 +386,36 @@ void test_layers(const std::string& golden_dir) {
         check(max_abs_diff(out.to_vector(), f.at("multihead/output").to_vector()) <= 1e-4, "multihead: output");
     }
 
+    // A head beyond the fused kernels' tiles (S = 200, d = 80): the layer runs it composed on the device
+    // and must agree with the reference's sequence of steps (src/transformer.cpp:279-304 and the backward
+    // lambdas of its nodes) evaluated by the CPU oracle.
+    {
+        engine::manual_seed(33);
+        const size_t B = 3, S = 200, D = 80;
+        Tensor q = Tensor::randn({B, S, D}, 0.0f, 1.0f, true), k = Tensor::randn({B, S, D}, 0.0f, 1.0f, true);
+        Tensor v = Tensor::randn({B, S, D}, 0.0f, 1.0f, true), g = Tensor::randn({B, S, D});
+        const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+        Tensor out = nn::scaled_dot_product_attention(q, k, v);
+        out.backward(g);
+        const std::vector<float> vq = q.to_vector(), vk = k.to_vector(), vv = v.to_vector(), vg = g.to_vector();
+        std::vector<float> sc(B * S * S), w(B * S * S), want(B * S * D), dw(B * S * S), ds(B * S * S);
+        std::vector<float> dq(B * S * D), dk(B * S * D), dv(B * S * D);
+        oracle_matmul_nt_f32(vq.data(), vk.data(), sc.data(), B, S, D, S, 1, 1, 0);
+        for (float& x : sc) x *= scale;
+        oracle_softmax_rows_f32(sc.data(), w.data(), B * S, S);
+        oracle_matmul_f32(w.data(), vv.data(), want.data(), B, S, S, D, 1, 1, 0);
+        oracle_matmul_nt_f32(vg.data(), vv.data(), dw.data(), B, S, D, S, 1, 1, 0);       // dW = g x v^T
+        oracle_matmul_tn_f32(w.data(), vg.data(), dv.data(), B, S, S, D, 1, 1, 0);        // dv = W^T x g
+        oracle_softmax_backward_f32(w.data(), dw.data(), ds.data(), B * S, S);
+        for (float& x : ds) x *= scale;
+        oracle_matmul_f32(ds.data(), vk.data(), dq.data(), B, S, S, D, 1, 1, 0);          // dq = dS x k
+        oracle_matmul_tn_f32(ds.data(), vq.data(), dk.data(), B, S, S, D, 1, 1, 0);       // dk = dS^T x q
+        check(scaled_error(out.to_vector(), want) <= 2e-5, "attention S=200 d=80 (composed on the device): output");
+        check(scaled_error(q.grad().to_vector(), dq) <= 4e-5, "attention S=200 d=80: gradient of Q");
+        check(scaled_error(k.grad().to_vector(), dk) <= 4e-5, "attention S=200 d=80: gradient of K");
+        check(scaled_error(v.grad().to_vector(), dv) <= 4e-5, "attention S=200 d=80: gradient of V");
+    }
+
     section("Linear: fused bias / ReLU and gradients");
     engine::manual_seed(21);
     Tensor x = Tensor::randn({4, 33, 96}, 0.0f, 1.0f, true);
