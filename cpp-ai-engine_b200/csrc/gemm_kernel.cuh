@@ -106,8 +106,9 @@ struct GemmParams {
     int a_vec_ok, b_vec_ok, c_vec_ok;
 };
 
-template <int BN, int BK, bool kPair = false>
+template <int BN, int BK, bool kPair = false, int kWW = kWorkerWarps>
 struct TileCfg {
+    static_assert(kWW == 8 || kWW == 16, "eight or sixteen worker warps");
     static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
     static_assert(BK == 16 || BK == 32, "unsupported k-block");
     static constexpr uint32_t kABytes = kBM * BK * 4;
@@ -120,7 +121,16 @@ struct TileCfg {
     static constexpr uint32_t kEpilogueBytes = kWorkerWarps * 4096;  // one 32 x 32 block per warp
     static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpilogueBytes + 1024;  // + alignment slack
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;           // two accumulators
-    static constexpr int kCols = BN / 2;                                  // columns per worker
+    // Four warps cover the 128 accumulator rows (a warp reads the 32 TMEM lanes of its quarter), so
+    // kWW / 4 warps share a row and split its columns.
+    static constexpr int kColParts = kWW / 4;
+    static constexpr int kCols = BN / kColParts;                          // columns per worker
+    static constexpr int kWorkerThreadsCfg = kWW * 32;
+    static constexpr int kThreadsCfg = kFirstWorkerWarp * 32 + kWW * 32;
+    // the epilogue's staging area (kEpilogueBytes in all) is cut into one slot per worker warp:
+    // 32 rows x kStageCols floats
+    static constexpr int kStageCols = (kEpilogueBytes / kWW) / (32 * 4);
+    static_assert(kStageCols == 32 || kStageCols == 16, "staging slot of 32 x 32 or 32 x 16 floats");
 };
 
 struct Work {
@@ -600,15 +610,19 @@ __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, i
 // kConv: 0 a plain product; 1 convolution forward (A gathered from x, NCHW store); 2 weight
 // gradient (both operands gathered, contraction over the output positions, plain store);
 // 3 input gradient (A gathered from dy, B from the weight, NCHW store).
-template <int BN, int BK, bool kTma, bool kPair = false, int kConv = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+// kWW: worker warps (8, or 16 for the large pair tiles: twice the warps per scheduler to hide the
+// latency of the split's and the drain's dependent instruction chains, half the accumulators each).
+template <int BN, int BK, bool kTma, bool kPair = false, int kConv = 0, int kWW = kWorkerWarps>
+__global__ void __launch_bounds__(kFirstWorkerWarp * 32 + kWW * 32, 1)
 gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                  const __grid_constant__ CUtensorMap mapB) {
-    using Cfg = TileCfg<BN, BK, kPair>;
+    using Cfg = TileCfg<BN, BK, kPair, kWW>;
+    constexpr int kWT = kWW * 32;  // worker threads
+    static_assert(kWW == kWorkerWarps || (kTma && kConv == 0), "sixteen workers: TMA loader, plain product");
     constexpr int kStages = Cfg::kStages;
     constexpr int kCols = Cfg::kCols;
     constexpr int kTileM = kPair ? 2 * kBM : kBM;        // rows of C per tile
-    constexpr int kArrivals = kPair ? 2 * kWorkerWarps : kWorkerWarps;
+    constexpr int kArrivals = kPair ? 2 * kWW : kWW;
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
     static_assert(!kPair || kTma, "pair mode loads with TMA");
     static_assert(kConv == 0 || !kTma, "the convolution gathers its operands in registers");
@@ -838,7 +852,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             bool ok = true;
             for (int w = first_work; w < p.total_work && ok; w += work_stride) {
                 const Work wk = decode_work(p, w);
-                target += kWorkerWarps;
+                target += kWW;
                 if (smem_load_acquire(cnt) < target) {
                     const uint64_t start = global_timer_ns();
                     for (;;) {
@@ -900,11 +914,19 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
       }
     } else {
         // ------------------------------------------------------------------ workers
-        if constexpr (kMoveRegs) reg_alloc<232>();
+        // setmaxnreg.inc can only take what setmaxnreg.dec released INSIDE THIS CTA (the pool is per CTA,
+        // not the SM's free registers), and blocks until it gets it: the control warpgroup's
+        // 128 x (launch - 40) registers must cover the workers' increase.
+        //   8 workers, 168 at launch: 128 x 128 = 16384 = 256 x (232 - 168)
+        //  16 workers,  96 at launch: 128 x 56  =  7168 >= 512 x (104 - 96) = 4096   (112 would need 8192: a hang)
+        constexpr int kWorkerRegs = kWW == 16 ? 104 : 232;
+        static_assert(kFirstWorkerWarp * 32 * ((kWW == 16 ? 96 : 168) - 40) >= kWT * (kWorkerRegs - (kWW == 16 ? 96 : 168)),
+                      "the workers' register increase exceeds what the control warpgroup releases");
+        if constexpr (kMoveRegs) reg_alloc<kWorkerRegs>();
         const int wid = warp - kFirstWorkerWarp;
         const int wtid = threadIdx.x - kFirstWorkerWarp * 32;
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*quarter .. +31
-        const int half = wid >> 2;     // which half of the tile's columns
+        const int half = wid >> 2;     // which part of the tile's columns (kWW / 4 parts)
         float acc[kCols];
         uint32_t it = 0, chain = 0;
         bool ok = true;
@@ -963,7 +985,17 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             tc_fence_after_sync();
             const uint32_t t0 = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN +
                                 half * kCols;
-            if constexpr (kCols >= 32) {
+            if constexpr (kCols >= 32 && kWW == 16) {
+                // 104 registers per thread: sixteen columns at a time
+#pragma unroll
+                for (int g = 0; g < kCols / 16; ++g) {
+                    uint32_t v[16];
+                    tmem_ld_x16(t0 + g * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[g * 16 + j] += __uint_as_float(v[j]);
+                }
+            } else if constexpr (kCols >= 32) {
 #pragma unroll
                 for (int g = 0; g < kCols / 32; ++g) {
                     uint32_t v[32];
@@ -1089,14 +1121,14 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         // (exact in fp32, then rounded to TF32) is written — one pass of
                         // shared-memory stores instead of two.
 #pragma unroll 4
-                        for (int q = wtid; q < kN4; q += kWorkerThreads) {
+                        for (int q = wtid; q < kN4; q += kWT) {
                             const float4 x = hi[q];
                             lo[q] = make_float4(tf32_tail_of_truncated(x.x), tf32_tail_of_truncated(x.y),
                                                 tf32_tail_of_truncated(x.z), tf32_tail_of_truncated(x.w));
                         }
                     } else {
 #pragma unroll 4
-                        for (int q = wtid; q < n4; q += kWorkerThreads) {
+                        for (int q = wtid; q < n4; q += kWT) {
                             const float4 x = hi[q];
                             float4 h, l;
                             tf32_split(x.x, h.x, l.x);
@@ -1181,11 +1213,16 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                 }
             } else {
-                float4* tile = reinterpret_cast<float4*>(smem + kStages * Cfg::kStageBytes) + wid * 256;
+                // staging slot of this warp: 32 rows x kSC floats, rows of kSC4 16-byte chunks
+                constexpr int kSC = Cfg::kStageCols;
+                constexpr int kSC4 = kSC / 4;
+                constexpr int kRowsPerStore = 32 / kSC4;  // rows one store instruction of the warp covers
+                constexpr int kStoreIters = 32 / kRowsPerStore;
+                float4* tile = reinterpret_cast<float4*>(smem + kStages * Cfg::kStageBytes) + wid * (8 * kSC);
                 const int row_base = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM + quarter * 32;
                 const int col_base = wk.nt * BN + half * kCols;
-                const int sub_row = lane >> 3;   // row within a group of four
-                const int chunk = lane & 7;      // 16-byte chunk of the 128-byte row segment
+                const int sub_row = lane / kSC4;  // row within the group one store instruction covers
+                const int chunk = lane % kSC4;    // 16-byte chunk of the row segment
                 const bool split_out = p.split_k > 1;
                 const float alpha = split_out ? 1.0f : p.alpha;
                 const float beta = split_out ? 0.0f : p.beta;
@@ -1203,18 +1240,18 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     : split_out ? ((long long)wk.sp * p.batch + wk.b) * (long long)p.M * p.N
                                 : (long long)wk.b * p.strideC;
 #pragma unroll
-                for (int g = 0; g < kCols / 32 + (kCols < 32 ? 1 : 0); ++g) {
-                    constexpr int kChunkCols = kCols < 32 ? kCols : 32;
+                for (int g = 0; g < kCols / kSC + (kCols < kSC ? 1 : 0); ++g) {
+                    constexpr int kChunkCols = kCols < kSC ? kCols : kSC;
                     constexpr int kChunks = kChunkCols / 4;
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < kChunks; ++j) {
-                        tile[lane * 8 + (j ^ (lane & 7))] =
-                            make_float4(acc[g * 32 + 4 * j], acc[g * 32 + 4 * j + 1],
-                                        acc[g * 32 + 4 * j + 2], acc[g * 32 + 4 * j + 3]);
+                        tile[lane * kSC4 + (j ^ (lane & (kSC4 - 1)))] =
+                            make_float4(acc[g * kSC + 4 * j], acc[g * kSC + 4 * j + 1],
+                                        acc[g * kSC + 4 * j + 2], acc[g * kSC + 4 * j + 3]);
                     }
                     __syncwarp();
-                    const int col = col_base + g * 32 + chunk * 4;
+                    const int col = col_base + g * kSC + chunk * 4;
                     if (chunk < kChunks && col < p.N && plain) {
                         // The common store — one destination (C or the split-K partials), no beta —
                         // apart from the general one below: a small product is one tile per
@@ -1230,11 +1267,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                             if (col + 3 < p.N) bias4.w = __ldg(p.bias + col + 3);
                         }
 #pragma unroll 1
-                        for (int it = 0; it < 8; ++it) {
-                            const int rr = it * 4 + sub_row;
+                        for (int it = 0; it < kStoreIters; ++it) {
+                            const int rr = it * kRowsPerStore + sub_row;
                             const int row = row_base + rr;
                             if (row >= p.M) continue;
-                            float4 v = tile[rr * 8 + (chunk ^ (rr & 7))];
+                            float4 v = tile[rr * kSC4 + (chunk ^ (rr & (kSC4 - 1)))];
                             v.x *= alpha;
                             v.y *= alpha;
                             v.z *= alpha;
@@ -1275,11 +1312,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         // 8 row groups) made the kernel 20 % slower at 4096^3 — the k-loop's
                         // code no longer stayed in the instruction cache.
 #pragma unroll 1
-                        for (int it = 0; it < 8; ++it) {
-                            const int rr = it * 4 + sub_row;
+                        for (int it = 0; it < kStoreIters; ++it) {
+                            const int rr = it * kRowsPerStore + sub_row;
                             const int row = row_base + rr;
                             if (row >= p.M) continue;
-                            float4 v = tile[rr * 8 + (chunk ^ (rr & 7))];
+                            float4 v = tile[rr * kSC4 + (chunk ^ (rr & (kSC4 - 1)))];
                             v.x *= alpha;
                             v.y *= alpha;
                             v.z *= alpha;

@@ -55,6 +55,7 @@ struct Options {
     long map_cache = 1;      // reuse encoded TMA tensor maps between calls
     long fwd_pace = -1;      // forwarder pause in ns per pair of chunks; -1 = automatic
     long fwd_mode = 0;       // 1 = forwarders follow the workers but copy nothing (measurement probe)
+    long pair_workers = 8;   // worker warps per CTA of the pair kernel: 8, or 16 (measured 3-5 % slower)
 };
 // Process-wide knobs, read without synchronisation on every call: set them while no other thread
 // is inside the library (they exist for benchmarking).
@@ -290,13 +291,17 @@ int launch_cfg(const GemmParams& params, const CUtensorMap& ma, const CUtensorMa
                                           stream, 1, p, ma, mb));
 }
 
-// CTA-pair kernel (tile 256 x 256): launched as clusters of two CTAs.
-int max_pair_clusters(int dev) {
+// CTA-pair kernel (tile 256 x 256): launched as clusters of two CTAs.  Two variants: eight worker
+// warps per CTA (default) or sixteen (option "pair_workers"; twice the warps per scheduler, half the
+// accumulators each — bit-identical results, measured 3-5 % slower at 4096^3 ... 16384^3: the
+// workers' instruction latency is not what binds the kernel).
+template <int WW>
+int max_pair_clusters_for(int dev) {
     static std::atomic<int> cached[kMaxDevices] = {};
     if (cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load(std::memory_order_relaxed);
     std::lock_guard<std::mutex> lock(g_mutex);
-    using Cfg = TileCfg<256, 32, true>;
-    auto kernel = gemm_tf32_kernel<256, 32, true, true>;
+    using Cfg = TileCfg<256, 32, true, WW>;
+    auto kernel = gemm_tf32_kernel<256, 32, true, true, 0, WW>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::kSmemBytes)) != cudaSuccess) {
         cudaGetLastError();
@@ -304,7 +309,7 @@ int max_pair_clusters(int dev) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreadsCfg, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -321,14 +326,23 @@ int max_pair_clusters(int dev) {
     cached[dev].store(n, std::memory_order_release);
     return n;
 }
+int max_pair_clusters(int dev) {
+    return g_opt.pair_workers == 16 ? max_pair_clusters_for<16>(dev) : max_pair_clusters_for<8>(dev);
+}
 
-int launch_pair(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
-                cudaStream_t stream) {
-    using Cfg = TileCfg<256, 32, true>;
+template <int WW>
+int launch_pair_for(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
+                    cudaStream_t stream) {
+    using Cfg = TileCfg<256, 32, true, WW>;
     GemmParams p = params;
     fill_schedule(p);
-    return static_cast<int>(launch_kernel(gemm_tf32_kernel<256, 32, true, true>, 2 * clusters, kThreads,
-                                          Cfg::kSmemBytes, stream, 2, p, ma, mb));
+    return static_cast<int>(launch_kernel(gemm_tf32_kernel<256, 32, true, true, 0, WW>, 2 * clusters,
+                                          Cfg::kThreadsCfg, Cfg::kSmemBytes, stream, 2, p, ma, mb));
+}
+int launch_pair(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
+                cudaStream_t stream) {
+    return g_opt.pair_workers == 16 ? launch_pair_for<16>(params, ma, mb, clusters, stream)
+                                    : launch_pair_for<8>(params, ma, mb, clusters, stream);
 }
 
 // Convolution kernels: register-staged loader with the implicit im2col gather (MODE 1 forward,
@@ -1663,6 +1677,9 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "fwd_mode")) {
         if (value < 0 || value > 1) return B200_EINVAL;
         g_opt.fwd_mode = value;
+    } else if (!std::strcmp(name, "pair_workers")) {
+        if (value != 8 && value != 16) return B200_EINVAL;
+        g_opt.pair_workers = value;
     } else if (!std::strcmp(name, "pdl")) {
         g_opt.pdl = value ? 1 : 0;
     } else if (!std::strcmp(name, "map_cache")) {
