@@ -80,8 +80,6 @@ struct GemmParams {
     int promote_every;  // k-blocks per TMEM accumulation chain
     int tf32_round;     // TF32 mode with the TMA loader: 1 = workers round the tile to nearest first
     int trunc_hi;       // 3xTF32 with the TMA loader: 1 = the head is the tensor core's own truncation
-    int fwd_pace_ns;    // forwarder warps: pause after each pair of chunks (spreads the peer stores over the tile time)
-    int fwd_mode;       // forwarder warps: 0 = copy tiles to the peers, 1 = follow the workers but copy nothing (probe)
     float* partial;     // split-K partials [split][batch][M][N] (split_k > 1)
     // fused epilogue: out = act(alpha*acc + beta*out + bias[col] + addend[row][col])
     const float* bias;    // N values, or null
@@ -874,7 +872,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const int row0 = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM;
                 const int col0 = wk.nt * BN;
                 const long long boff = (long long)wk.b * p.strideC;
-                if (p.fwd_mode == 1) continue;
                 if (p.c_vec_ok && (p.N & 3) == 0) {
                     constexpr int kC4 = BN / 4;              // 16-byte chunks per tile row
                     constexpr int kPasses = kBM * kC4 / 64;  // chunks per forwarder thread
@@ -897,7 +894,6 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                             if (in0) *reinterpret_cast<float4*>(dst + off0) = v0;
                             if (in1) *reinterpret_cast<float4*>(dst + off1) = v1;
                         }
-                        if (p.fwd_pace_ns > 0) __nanosleep(p.fwd_pace_ns);
                     }
                 } else {
                     for (int u = ftid; u < kBM * BN; u += 64) {

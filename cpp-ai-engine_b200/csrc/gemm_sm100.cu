@@ -53,8 +53,6 @@ struct Options {
     long head_mode = 0;      // 3xTF32 head: 0 = rounded to nearest by the workers, 1 = the tensor core's truncation
     long pdl = 1;            // launch with programmatic stream serialization (set-up overlaps the previous kernel)
     long map_cache = 1;      // reuse encoded TMA tensor maps between calls
-    long fwd_pace = -1;      // forwarder pause in ns per pair of chunks; -1 = automatic
-    long fwd_mode = 0;       // 1 = forwarders follow the workers but copy nothing (measurement probe)
     long pair_workers = 8;   // worker warps per CTA of the pair kernel: 8, or 16 (measured 3-5 % slower)
 };
 // Process-wide knobs, read without synchronisation on every call: set them while no other thread
@@ -679,8 +677,6 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
     p.promote_every = promote_interval(precision);
     p.tf32_round = g_opt.tf32_round ? 1 : 0;
     p.trunc_hi = g_opt.head_mode == 1 ? 1 : 0;
-    p.fwd_pace_ns = g_opt.fwd_pace >= 0 ? static_cast<int>(g_opt.fwd_pace) : 0;
-    p.fwd_mode = static_cast<int>(g_opt.fwd_mode);
     p.partial = static_cast<float*>(workspace);
     p.status = st.status;
     if (ep != nullptr) {
@@ -1671,12 +1667,6 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "head_mode")) {
         if (value < 0 || value > 1) return B200_EINVAL;
         g_opt.head_mode = value;
-    } else if (!std::strcmp(name, "fwd_pace")) {
-        if (value < -1 || value > 100000) return B200_EINVAL;
-        g_opt.fwd_pace = value;
-    } else if (!std::strcmp(name, "fwd_mode")) {
-        if (value < 0 || value > 1) return B200_EINVAL;
-        g_opt.fwd_mode = value;
     } else if (!std::strcmp(name, "pair_workers")) {
         if (value != 8 && value != 16) return B200_EINVAL;
         g_opt.pair_workers = value;

@@ -420,10 +420,6 @@ uint64_t b200_gemm_launch_count(void);
  *                   store pass less; representation error 2^-21 instead of 2^-22 per operand)
  *   "pair_workers"  worker warps per CTA of the CTA-pair kernel: 8 (default) or 16 (same bits; measured 3-5 %
  *                   slower on a B200)
- *   "fwd_pace"      column-sharded products: nanoseconds the forwarder warps pause after each pair of 16-byte
- *                   chunks (-1 / 0 = no pause; pauses only delayed the last tile's copies when measured)
- *   "fwd_mode"      1 = the forwarder warps follow the workers but copy nothing (measurement probe: the peers'
- *                   C stays unwritten), 0 (default) = copy
  *   "pdl"           1 (default) = kernels are launched with programmatic stream serialization: the
  *                   set-up of a product overlaps the end of the kernel before it; 0 = plain launches
  *   "map_cache"     1 (default) = encoded TMA tensor maps are reused between calls with the same
