@@ -1362,6 +1362,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             if constexpr (kConv == 0) {
                 // this warp's part of the tile is in C: the forwarders may copy it to the peers
                 if (p.n_dest > 1) {
+                    __threadfence();  // the tile's stores have reached L2, where the forwarders read them
                     __syncwarp();
                     if (lane == 0) smem_add_release(smem_u32(&fwd_count_s), 1u);
                 }

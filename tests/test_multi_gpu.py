@@ -33,7 +33,10 @@ def _rank_main(rank, world, port, mode, M, N, K, results):
         g = orc.Rng(1)  # the reference generator: same bytes on every rank
         a, b = g.randn((M, K), 0.0, K ** -0.5), g.randn((K, N), 0.0, K ** -0.5)
         A, B = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
-        whole = pkg.matmul(A, B)
+        # the one-GPU product without workspace, i.e. never K-split: the column blocks of the sharded call
+        # (which never splits either) then add every element's terms in the same order
+        whole = torch.empty((M, N), device=dev)
+        pkg.gemm(A, B, whole, batch=1, M=M, N=N, K=K, lda=K, ldb=N, ldc=N)
         pkg.status()
         ok = {}
         if mode in ("fused", "nccl"):
@@ -86,8 +89,9 @@ def _rank_main(rank, world, port, mode, M, N, K, results):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("shape", [(1024, 2048, 512), (768, 1000, 300)])  # even shards; ragged: 512 + 488 columns
 @pytest.mark.parametrize("mode", ["nccl", "fused", "host"])
-def test_two_gpu_column_shards(cuda, mode):
+def test_two_gpu_column_shards(cuda, mode, shape):
     import torch
     import torch.multiprocessing as mp
 
@@ -99,7 +103,7 @@ def test_two_gpu_column_shards(cuda, mode):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         results = mgr.dict()
-        procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, 1024, 2048, 512, results)) for r in range(2)]
+        procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, *shape, results)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:

@@ -22,6 +22,7 @@ kernels reproduce it bit for bit, their products being exact and their order the
 sum leaves a different one, and Adam's normalisation g / (|g| + 1e-8) turns that residue into a step of
 up to a tenth of the learning rate per iteration.  The same run under SGD agrees to 1e-7.  That line
 may report a drift of up to 5 steps x lr = 5e-2; every other line must be ``[ ok ]``."""
+import os
 import re
 import subprocess
 from pathlib import Path
@@ -42,8 +43,9 @@ def test_reference_parity_suite_over_the_new_kernels(cuda):
         pytest.skip("oracle/_ref_cuda/test_engine_seam was not built (needs the reference's source tree)")
     proc = subprocess.run([str(EXE)], capture_output=True, text=True, timeout=900)
     out = proc.stdout
-    (ROOT / "gpurun_out").mkdir(exist_ok=True)
-    (ROOT / "gpurun_out" / "reference_seam_suite.log").write_text(out + "\n--- stderr ---\n" + proc.stderr)
+    log = os.environ.get("B200_SEAM_SUITE_LOG")  # optional: keep the suite's full output in a file
+    if log:
+        Path(log).write_text(out + "\n--- stderr ---\n" + proc.stderr)
     print(out[-6000:])
     assert "CPU / GPU parity" in out and "no kernel was launched" not in out
     ok_lines = [ln for ln in out.splitlines() if ln.startswith("  [ ok ]")]
