@@ -97,8 +97,10 @@ struct GemmParams {
     int tail_tiles;     // > 0: partials are compact, [split][tail tile][tile rows][BN]
     int* status;
     // tensor-core view of the shared-memory tiles
-    uint32_t a_lbo, a_sbo, a_kstep, a_layout;
-    uint32_t b_lbo, b_sbo, b_kstep, b_layout;
+    // k-step ks (8 values of k) of an operand tile starts (ks / 4) * ksub + (ks % 4) * kstep bytes into it:
+    // a K-major tile wider than one 128-byte swizzle row (BK = 64) is two 32-wide sub-tiles side by side
+    uint32_t a_lbo, a_sbo, a_kstep, a_ksub, a_layout;
+    uint32_t b_lbo, b_sbo, b_kstep, b_ksub, b_layout;
     uint32_t idesc;
     // loader / epilogue fast paths
     int a_vec_ok, b_vec_ok, c_vec_ok;
@@ -108,7 +110,7 @@ template <int BN, int BK, bool kPair = false, int kWW = kWorkerWarps>
 struct TileCfg {
     static_assert(kWW == 8 || kWW == 16, "eight or sixteen worker warps");
     static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
-    static_assert(BK == 16 || BK == 32, "unsupported k-block");
+    static_assert(BK == 16 || BK == 32 || BK == 64, "unsupported k-block");
     static constexpr uint32_t kABytes = kBM * BK * 4;
     static constexpr int kBCols = kPair ? BN / 2 : BN;  // B columns held by one CTA
     static constexpr uint32_t kBBytes = kBCols * BK * 4;
@@ -723,15 +725,19 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     mbar_arrive_expect_tx(full, Cfg::kHalf);
                     const int row0 = wk.mt * kTileM + static_cast<int>(cta_rank) * kBM;
                     const int col0 = wk.nt * BN + static_cast<int>(cta_rank) * Cfg::kBCols;
-                    if (!p.transA) {
-                        tma_load_3d(sa, &mapA, full, kb * BK, row0, za);
+                    if (!p.transA) {  // K-major: one box of 32 k per 128-byte swizzle row
+#pragma unroll
+                        for (int h = 0; h < (BK + 31) / 32; ++h)
+                            tma_load_3d(sa + h * (kBM * 128), &mapA, full, kb * BK + h * 32, row0, za);
                     } else {
 #pragma unroll
                         for (int j = 0; j < kBM / 32; ++j)
                             tma_load_3d(sa + j * (BK * 128), &mapA, full, row0 + j * 32, kb * BK, za);
                     }
                     if (p.transB) {
-                        tma_load_3d(sb, &mapB, full, kb * BK, col0, zb);
+#pragma unroll
+                        for (int h = 0; h < (BK + 31) / 32; ++h)
+                            tma_load_3d(sb + h * (Cfg::kBCols * 128), &mapB, full, kb * BK + h * 32, col0, zb);
                     } else {
 #pragma unroll
                         for (int j = 0; j < Cfg::kBCols / 32; ++j)
@@ -754,7 +760,11 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             const uint32_t s0 = smem_u32(smem);
             const uint64_t dA_hi = make_smem_desc(s0, p.a_lbo, p.a_sbo, p.a_layout);
             const uint64_t dB_hi = make_smem_desc(s0 + Cfg::kABytes, p.b_lbo, p.b_sbo, p.b_layout);
-            const uint32_t ka = p.a_kstep >> 4, kb_step = p.b_kstep >> 4;
+            // descriptor offset (16-byte units) of k-step ks within an operand tile
+            const uint32_t a_kstep = p.a_kstep >> 4, a_ksub = p.a_ksub >> 4;
+            const uint32_t b_kstep = p.b_kstep >> 4, b_ksub = p.b_ksub >> 4;
+            auto a_off = [&](int ks) { return static_cast<uint32_t>(ks >> 2) * a_ksub + static_cast<uint32_t>(ks & 3) * a_kstep; };
+            auto b_off = [&](int ks) { return static_cast<uint32_t>(ks >> 2) * b_ksub + static_cast<uint32_t>(ks & 3) * b_kstep; };
             constexpr uint32_t kLoOff = Cfg::kHalf >> 4;
             const uint32_t idesc = p.idesc;
             auto issue_mma = [](uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t accum) {
@@ -812,8 +822,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                         // tiny, so that only the BK/8 head products truncate at full scale.
 #pragma unroll
                         for (int ks = 0; ks < BK / 8; ++ks) {
-                            const uint64_t ah = dA_hi + (soff + ks * ka);
-                            const uint64_t bh = dB_hi + (soff + ks * kb_step);
+                            const uint64_t ah = dA_hi + (soff + a_off(ks));
+                            const uint64_t bh = dB_hi + (soff + b_off(ks));
                             issue_mma(d, ah + kLoOff, bh, idesc, accumulate);
                             issue_mma(d, ah, bh + kLoOff, idesc, 1u);
                             accumulate = 1u;
@@ -821,8 +831,8 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ++ks) {
-                        const uint64_t ah = dA_hi + (soff + ks * ka);
-                        const uint64_t bh = dB_hi + (soff + ks * kb_step);
+                        const uint64_t ah = dA_hi + (soff + a_off(ks));
+                        const uint64_t bh = dB_hi + (soff + b_off(ks));
                         issue_mma(d, ah, bh, idesc, accumulate);
                         accumulate = 1u;
                     }

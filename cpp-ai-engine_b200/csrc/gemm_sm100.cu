@@ -53,6 +53,7 @@ struct Options {
     long head_mode = 0;      // 3xTF32 head: 0 = rounded to nearest by the workers, 1 = the tensor core's truncation
     long pdl = 1;            // launch with programmatic stream serialization (set-up overlaps the previous kernel)
     long map_cache = 1;      // reuse encoded TMA tensor maps between calls
+    long block_k = 0;        // values of k per pipeline stage: 0 = automatic, 32, or 64 (TMA loader, tiles up to 64 wide)
     long pair_workers = 8;   // worker warps per CTA of the pair kernel: 8, or 16 (measured 3-5 % slower)
 };
 // Process-wide knobs, read without synchronisation on every call: set them while no other thread
@@ -115,7 +116,7 @@ int device_state(DeviceState** out) {
 
 struct OperandMap {
     CUtensorMap map;
-    uint32_t lbo, sbo, kstep, layout;
+    uint32_t lbo, sbo, kstep, ksub, layout;
 };
 
 // Describes one operand tile to TMA (how to fetch it) and to the tensor core (how it lies in
@@ -137,13 +138,17 @@ int make_operand_map(OperandMap* om, const float* base, bool k_contig, int64_t r
     if (k_contig) {
         dims[0] = static_cast<cuuint64_t>(K);
         dims[1] = static_cast<cuuint64_t>(rows_total);
-        box[0] = bk;
+        // a row of the box is one swizzle row: at most 32 floats (128 bytes); a wider k-block is
+        // fetched as several boxes side by side
+        const int box_k = bk >= 32 ? 32 : bk;
+        box[0] = box_k;
         box[1] = tile_rows;
-        swz = (bk == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-        om->layout = (bk == 32) ? kLayoutSw128 : kLayoutSw64;
+        swz = (box_k == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+        om->layout = (box_k == 32) ? kLayoutSw128 : kLayoutSw64;
         om->lbo = 16;
-        om->sbo = 8u * bk * 4u;  // eight rows
-        om->kstep = 32;          // 8 floats along the row
+        om->sbo = 8u * box_k * 4u;    // eight rows
+        om->kstep = 32;               // 8 floats along the row
+        om->ksub = tile_rows * 128u;  // the next 32 values of k: the next sub-tile
     } else {
         dims[0] = static_cast<cuuint64_t>(rows_total);
         dims[1] = static_cast<cuuint64_t>(K);
@@ -154,6 +159,7 @@ int make_operand_map(OperandMap* om, const float* base, bool k_contig, int64_t r
         om->lbo = bk * 128u;      // next 32 m|n: next box
         om->sbo = 512;            // next 4 k: four 128-byte rows
         om->kstep = 1024;         // 8 k
+        om->ksub = 4096;          // 32 k: the rows of a box simply continue
     }
     dims[2] = static_cast<cuuint64_t>(nbatch);
     box[2] = 1;
@@ -430,6 +436,12 @@ int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& m
     case BN_:                                                                              \
         if (!tma) return launch_cfg<BN_, 32, false>(p, ma, mb, grid, stream);              \
         return launch_cfg<BN_, 32, true>(p, ma, mb, grid, stream);
+    if (bk == 64) {
+        if (!tma) return B200_EINVAL;
+        if (bn == 32) return launch_cfg<32, 64, true>(p, ma, mb, grid, stream);
+        if (bn == 64) return launch_cfg<64, 64, true>(p, ma, mb, grid, stream);
+        return B200_EINVAL;
+    }
     switch (bn) {
         B200_CASE(32)
         B200_CASE(64)
@@ -441,6 +453,8 @@ int dispatch(int bn, int bk, bool tma, const GemmParams& p, const CUtensorMap& m
 #undef B200_CASE
 }
 
+
+constexpr bool kAutoBlockK64 = false;  // automatic choice of 64-wide k-blocks (see make_plan)
 
 struct Plan {
     int bn, bk, split_k, kb_per_split, kblocks, tiles_m, tiles_n;
@@ -533,6 +547,10 @@ Plan make_plan(const DeviceState& st, int64_t batch, int64_t M, int64_t N, int64
     pl.pair = pair;
     if (pl.pair) pl.tiles_m = ceil_div(M, 2 * kBM);
     pl.tiles_n = ceil_div(N, bn);
+    // Narrow tiles are latency-bound: their k-loop is a chain of barrier hand-overs per k-block, so
+    // 64 values of k per stage (two swizzle rows side by side) halve the hand-overs.  TMA loader only.
+    const bool bk64_legal = pl.tma && !pl.pair && bn <= 64;
+    if (bk64_legal && (g_opt.block_k == 64 || (g_opt.block_k == 0 && kAutoBlockK64 && K >= 256))) pl.bk = 64;
     pl.kblocks = ceil_div(K, pl.bk);
     // Deterministic split-K for tall-skinny products (few output tiles, long K).
     pl.split_k = 1;
@@ -711,10 +729,12 @@ int gemm_impl(DeviceState& st, const float* A, const float* B, float* const* des
         p.a_lbo = oa.lbo;
         p.a_sbo = oa.sbo;
         p.a_kstep = oa.kstep;
+        p.a_ksub = oa.ksub;
         p.a_layout = oa.layout;
         p.b_lbo = ob.lbo;
         p.b_sbo = ob.sbo;
         p.b_kstep = ob.kstep;
+        p.b_ksub = ob.ksub;
         p.b_layout = ob.layout;
         p.idesc = make_idesc_tf32(pl.pair ? 2 * kBM : kBM, pl.bn, a_k_contig ? 0 : 1,
                                   b_k_contig ? 0 : 1);
@@ -1667,6 +1687,9 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "head_mode")) {
         if (value < 0 || value > 1) return B200_EINVAL;
         g_opt.head_mode = value;
+    } else if (!std::strcmp(name, "block_k")) {
+        if (value != 0 && value != 32 && value != 64) return B200_EINVAL;
+        g_opt.block_k = value;
     } else if (!std::strcmp(name, "pair_workers")) {
         if (value != 8 && value != 16) return B200_EINVAL;
         g_opt.pair_workers = value;

@@ -418,6 +418,9 @@ uint64_t b200_gemm_launch_count(void);
  *                   nearest TF32 head and write head and tail; 1 = the tensor core's own truncation
  *                   of the raw tile is the head and only the tail is written (one shared-memory
  *                   store pass less; representation error 2^-21 instead of 2^-22 per operand)
+ *   "block_k"       values of k per pipeline stage: 0 / 32 = 32 (default), 64 = two 128-byte swizzle rows side by
+ *                   side for tiles up to 64 columns wide with the TMA loader (half the barrier hand-overs of the
+ *                   k-loop; measured 3-5 % faster at K >= 384, slower at K = 96, error 1.2-1.6x: not the default)
  *   "pair_workers"  worker warps per CTA of the CTA-pair kernel: 8 (default) or 16 (same bits; measured 3-5 %
  *                   slower on a B200)
  *   "pdl"           1 (default) = kernels are launched with programmatic stream serialization: the
