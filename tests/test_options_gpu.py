@@ -30,7 +30,7 @@ def test_pair_kernel_with_sixteen_worker_warps_is_bit_identical(pkg, orc, cuda, 
     import torch
 
     g = orc.Rng(70)
-    for M, N, K in ((1024, 768, 320), (2048, 2048, 512)):
+    for M, N, K in ((2048, 2048, 512), (4000, 4100, 256)):  # whole and ragged 256 x 256 tiles
         a, b = g.randn((M, K)), g.randn((K, N))
         A, B = dev(a, cuda), dev(b, cuda)
         want = product(pkg, cuda, A, B, M, N, K, lda=K, ldb=N)
