@@ -82,3 +82,27 @@ def test_fused_multi_destination_stores(pkg, orc, cuda):
     whole = pkg.matmul(A, B)
     pkg.status()
     assert torch.equal(whole, dests[0])
+
+
+@pytest.mark.parametrize("M,N,K", [(12288, 4096, 256), (25600, 768, 100), (1000, 1056, 72)])
+def test_eight_destinations_several_tiles_per_cta(pkg, cuda, M, N, K):
+    """Eight shards into eight destination buffers, the widest gather the library accepts, on shapes
+    whose shards give a CTA more than one tile (CTA pairs; single CTAs; a ragged small one), so that
+    the forwarder warps follow the workers across tiles: every buffer ends bit-identical to the
+    unsharded product."""
+    import torch
+
+    gen = torch.Generator(device="cpu").manual_seed(M + N + K)
+    A = torch.randn((M, K), generator=gen).to(cuda)
+    B = torch.randn((K, N), generator=gen).to(cuda)
+    dests = [torch.full((M, N), float("nan"), device=cuda) for _ in range(8)]
+    for rank in range(8):
+        col0, cols = pkg.shard.column_shard(N, 8, rank)
+        # each "rank" lists its own buffer first, as the sharded call does
+        order = dests[rank:] + dests[:rank]
+        pkg.gemm_colshard(A, B, order, M=M, N=N, K=K, col0=col0, cols=cols, lda=K, ldb=N, ldc=N)
+    pkg.status()
+    whole = pkg.matmul(A, B)
+    pkg.status()
+    for d in dests:
+        assert torch.equal(d, whole)
