@@ -1001,6 +1001,20 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[g * 16 + j] += __uint_as_float(v[j]);
                 }
+            } else if constexpr (kCols >= 64) {
+                // Two 32-column loads in flight per wait: the load's latency is paid once per 64 columns
+                // (the registers allow no more beside 128 accumulators).
+#pragma unroll
+                for (int g = 0; g < kCols / 64; ++g) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_x32(t0 + g * 64, v0);
+                    tmem_ld_x32(t0 + g * 64 + 32, v1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[g * 64 + j] += __uint_as_float(v0[j]);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[g * 64 + 32 + j] += __uint_as_float(v1[j]);
+                }
             } else if constexpr (kCols >= 32) {
 #pragma unroll
                 for (int g = 0; g < kCols / 32; ++g) {
@@ -1121,28 +1135,44 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     // TF32 mode without rounding: the tensor core reads the fp32 tile as it is
                     // (it drops the low 13 mantissa bits), so the workers only pass the stage on.
                     const int n4 = (prec3 || p.tf32_round) ? kN4 : 0;
-                    if (prec3 && p.trunc_hi) {
-                        // The raw tile stays as it is: the tensor core drops the low 13 mantissa bits
-                        // of what it reads, so its head is trunc(x); only the tail x - trunc(x)
-                        // (exact in fp32, then rounded to TF32) is written — one pass of
-                        // shared-memory stores instead of two.
-#pragma unroll 4
-                        for (int q = wtid; q < kN4; q += kWT) {
-                            const float4 x = hi[q];
-                            lo[q] = make_float4(tf32_tail_of_truncated(x.x), tf32_tail_of_truncated(x.y),
-                                                tf32_tail_of_truncated(x.z), tf32_tail_of_truncated(x.w));
-                        }
-                    } else {
-#pragma unroll 4
-                        for (int q = wtid; q < n4; q += kWT) {
-                            const float4 x = hi[q];
-                            float4 h, l;
-                            tf32_split(x.x, h.x, l.x);
-                            tf32_split(x.y, h.y, l.y);
-                            tf32_split(x.z, h.z, l.z);
-                            tf32_split(x.w, h.w, l.w);
-                            hi[q] = h;
-                            if (prec3) lo[q] = l;
+                    // A thread's chunks are loaded first, up to eight at a time, and split and stored
+                    // afterwards: written as one loop (load, split, store, next chunk) the stores of one
+                    // chunk may alias the load of the next as far as the compiler can tell, and every
+                    // chunk paid a full shared-memory round trip — most of a narrow tile's k-block.
+                    constexpr int kPer = (kN4 + kWT - 1) / kWT;  // chunks per thread
+                    constexpr int kBatch = kPer < 8 ? kPer : 8;
+                    const bool tail_only = prec3 && p.trunc_hi;
+                    if (n4 != 0) {
+#pragma unroll
+                        for (int u0 = 0; u0 < kPer; u0 += kBatch) {
+                            float4 x[kBatch];
+#pragma unroll
+                            for (int u = 0; u < kBatch; ++u) {
+                                const int q = wtid + (u0 + u) * kWT;
+                                if (u0 + u < kPer && ((u0 + u + 1) * kWT <= kN4 || q < kN4)) x[u] = hi[q];
+                            }
+#pragma unroll
+                            for (int u = 0; u < kBatch; ++u) {
+                                const int q = wtid + (u0 + u) * kWT;
+                                if (u0 + u < kPer && ((u0 + u + 1) * kWT <= kN4 || q < kN4)) {
+                                    if (tail_only) {
+                                        // The raw tile stays as it is: the tensor core drops the low 13
+                                        // mantissa bits of what it reads, so its head is trunc(x); only the
+                                        // tail x - trunc(x) (exact in fp32, then rounded to TF32) is written —
+                                        // one pass of shared-memory stores instead of two.
+                                        lo[q] = make_float4(tf32_tail_of_truncated(x[u].x), tf32_tail_of_truncated(x[u].y),
+                                                            tf32_tail_of_truncated(x[u].z), tf32_tail_of_truncated(x[u].w));
+                                    } else {
+                                        float4 h, l;
+                                        tf32_split(x[u].x, h.x, l.x);
+                                        tf32_split(x[u].y, h.y, l.y);
+                                        tf32_split(x[u].z, h.z, l.z);
+                                        tf32_split(x[u].w, h.w, l.w);
+                                        hi[q] = h;
+                                        if (prec3) lo[q] = l;
+                                    }
+                                }
+                            }
                         }
                     }
                 } else {
