@@ -607,22 +607,75 @@ __device__ __forceinline__ void conv_weight_T_split_store(const GemmParams& p, i
     }
 }
 
+// Splits one landed stage in place: the raw fp32 tile becomes the head tile, the tail tile is written
+// kHalf bytes further on.  kN4 16-byte chunks are shared out over kT threads.  A thread's chunks are
+// loaded first, up to kMaxBatch at a time, and split and stored afterwards: written as one loop
+// (load, split, store, next chunk) the stores of one chunk may alias the load of the next as far as
+// the compiler can tell, and every chunk would pay a full shared-memory round trip.
+template <int kN4, int kT, int kMaxBatch>
+__device__ __forceinline__ void split_stage(float4* hi, float4* lo, int tid, bool prec3, bool tail_only) {
+    constexpr int kPer = (kN4 + kT - 1) / kT;  // chunks per thread
+    constexpr int kBatch = kPer < kMaxBatch ? kPer : kMaxBatch;
+#pragma unroll
+    for (int u0 = 0; u0 < kPer; u0 += kBatch) {
+        float4 x[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int q = tid + (u0 + u) * kT;
+            if (u0 + u < kPer && ((u0 + u + 1) * kT <= kN4 || q < kN4)) x[u] = hi[q];
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int q = tid + (u0 + u) * kT;
+            if (u0 + u < kPer && ((u0 + u + 1) * kT <= kN4 || q < kN4)) {
+                if (tail_only) {
+                    // The raw tile stays as it is: the tensor core drops the low 13 mantissa bits of
+                    // what it reads, so its head is trunc(x); only the tail x - trunc(x) (exact in
+                    // fp32, then rounded to TF32) is written — one pass of shared-memory stores
+                    // instead of two.
+                    lo[q] = make_float4(tf32_tail_of_truncated(x[u].x), tf32_tail_of_truncated(x[u].y),
+                                        tf32_tail_of_truncated(x[u].z), tf32_tail_of_truncated(x[u].w));
+                } else {
+                    float4 h, l;
+                    tf32_split(x[u].x, h.x, l.x);
+                    tf32_split(x[u].y, h.y, l.y);
+                    tf32_split(x[u].z, h.z, l.z);
+                    tf32_split(x[u].w, h.w, l.w);
+                    hi[q] = h;
+                    if (prec3) lo[q] = l;
+                }
+            }
+        }
+    }
+}
+
 // kConv: 0 a plain product; 1 convolution forward (A gathered from x, NCHW store); 2 weight
 // gradient (both operands gathered, contraction over the output positions, plain store);
 // 3 input gradient (A gathered from dy, B from the weight, NCHW store).
 // kWW: worker warps (8, or 16 for the large pair tiles: twice the warps per scheduler to hide the
 // latency of the split's and the drain's dependent instruction chains, half the accumulators each).
-template <int BN, int BK, bool kTma, bool kPair = false, int kConv = 0, int kWW = kWorkerWarps>
-__global__ void __launch_bounds__(kFirstWorkerWarp * 32 + kWW * 32, 1)
+// kSW: warps that do nothing but split the landed stages (0, or 8 for the pair tiles).  With them the kWW
+// worker warps only drain the accumulator and store: the two dependent chains of a k-block — split,
+// hand over to the tensor core; wait for it, add its partial sum into registers — run side by side
+// on different warps instead of one after the other in each worker.
+template <int BN, int BK, bool kTma, bool kPair = false, int kConv = 0, int kWW = kWorkerWarps, int kSW = 0>
+__global__ void __launch_bounds__((kFirstWorkerWarp + kWW + kSW) * 32, 1)
 gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                  const __grid_constant__ CUtensorMap mapB) {
     using Cfg = TileCfg<BN, BK, kPair, kWW>;
     constexpr int kWT = kWW * 32;  // worker threads
     static_assert(kWW == kWorkerWarps || (kTma && kConv == 0), "sixteen workers: TMA loader, plain product");
+    static_assert(kSW == 0 || (kSW == 8 && kWW == 8 && kTma && kConv == 0 && BN == 256),
+                  "split warps: TMA loader, plain product, 256-wide tiles");
+    // registers per thread at launch (what ptxas reports for the launch bounds) and of a split warp
+    constexpr int kLaunchRegs = (kSW > 0 || kWW == 16) ? 96 : 168;
+    constexpr int kSplitRegs = 40;
+    constexpr int kSplitters = kSW > 0 ? kSW : kWW;  // warps that hand a split stage to the tensor core
     constexpr int kStages = Cfg::kStages;
     constexpr int kCols = Cfg::kCols;
     constexpr int kTileM = kPair ? 2 * kBM : kBM;        // rows of C per tile
     constexpr int kArrivals = kPair ? 2 * kWW : kWW;
+    constexpr int kSplitArrivals = kPair ? 2 * kSplitters : kSplitters;
     static_assert(kTma || BK == 32, "the register-staged loader writes 128-byte rows");
     static_assert(!kPair || kTma, "pair mode loads with TMA");
     static_assert(kConv == 0 || !kTma, "the convolution gathers its operands in registers");
@@ -654,7 +707,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
-            mbar_init(smem_u32(&split_bar[s]), kArrivals);
+            mbar_init(smem_u32(&split_bar[s]), kSplitArrivals);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -918,16 +971,56 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
             }
         }
       }
+    } else if (kSW > 0 && warp >= kFirstWorkerWarp + kWW) {
+        // ------------------------------------------------------------------ split warps
+        if constexpr (kSW > 0) {
+            reg_dealloc<kSplitRegs>();
+            constexpr int kST = kSW * 32;
+            const int stid = static_cast<int>(threadIdx.x) - (kFirstWorkerWarp + kWW) * 32;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = first_work; w < p.total_work && ok; w += work_stride) {
+                const Work wk = decode_work(p, w);
+                for (int kb = wk.kb0; kb < wk.kb1; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    bool got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status, kStatWorkerFull);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * Cfg::kStageBytes;
+                    constexpr int kN4 = Cfg::kHalf / 16;
+                    if (prec3 || p.tf32_round)
+                        split_stage<kN4, kST, 4>(reinterpret_cast<float4*>(stage),
+                                                 reinterpret_cast<float4*>(stage + Cfg::kHalf), stid, prec3,
+                                                 prec3 && p.trunc_hi);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (kPair) {
+                            mbar_arrive_cluster(map_to_cta(smem_u32(&split_bar[s]), 0));
+                        } else {
+                            mbar_arrive(smem_u32(&split_bar[s]));
+                        }
+                    }
+                }
+            }
+            grid_launch_dependents();
+        }
     } else {
         // ------------------------------------------------------------------ workers
         // setmaxnreg.inc can only take what setmaxnreg.dec released INSIDE THIS CTA (the pool is per CTA,
-        // not the SM's free registers), and blocks until it gets it: the control warpgroup's
-        // 128 x (launch - 40) registers must cover the workers' increase.
+        // not the SM's free registers), and blocks until it gets it: what the control warpgroup (and the
+        // split warps) give up must cover the workers' increase.
         //   8 workers, 168 at launch: 128 x 128 = 16384 = 256 x (232 - 168)
         //  16 workers,  96 at launch: 128 x 56  =  7168 >= 512 x (104 - 96) = 4096   (112 would need 8192: a hang)
-        constexpr int kWorkerRegs = kWW == 16 ? 104 : 232;
-        static_assert(kFirstWorkerWarp * 32 * ((kWW == 16 ? 96 : 168) - 40) >= kWT * (kWorkerRegs - (kWW == 16 ? 96 : 168)),
-                      "the workers' register increase exceeds what the control warpgroup releases");
+        //   8 workers + 8 split warps, 96 at launch: 128 x 56 + 256 x 56 = 21504 >= 256 x (176 - 96) = 20480
+        constexpr int kWorkerRegs = kSW > 0 ? 176 : kWW == 16 ? 104 : 232;
+        static_assert(kFirstWorkerWarp * 32 * (kLaunchRegs - 40) + kSW * 32 * (kLaunchRegs - kSplitRegs) >=
+                          kWT * (kWorkerRegs - kLaunchRegs),
+                      "the workers' register increase exceeds what the other warps release");
         if constexpr (kMoveRegs) reg_alloc<kWorkerRegs>();
         const int wid = warp - kFirstWorkerWarp;
         const int wtid = threadIdx.x - kFirstWorkerWarp * 32;
@@ -1001,7 +1094,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[g * 16 + j] += __uint_as_float(v[j]);
                 }
-            } else if constexpr (kCols >= 64) {
+            } else if constexpr (kCols >= 64 && kSW == 0) {
                 // Two 32-column loads in flight per wait: the load's latency is paid once per 64 columns
                 // (the registers allow no more beside 128 accumulators).
 #pragma unroll
@@ -1118,7 +1211,9 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                 const uint32_t s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
                 uint8_t* stage = smem + s * Cfg::kStageBytes;
-                if constexpr (kTma) {
+                if constexpr (kSW > 0) {
+                    // the split warps hand the stages over; these warps only drain
+                } else if constexpr (kTma) {
                     bool got;
                     {
                         got = wait_bar(smem_u32(&full_bar[s]), ph, abort_flag, p.status,
@@ -1135,46 +1230,7 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     // TF32 mode without rounding: the tensor core reads the fp32 tile as it is
                     // (it drops the low 13 mantissa bits), so the workers only pass the stage on.
                     const int n4 = (prec3 || p.tf32_round) ? kN4 : 0;
-                    // A thread's chunks are loaded first, up to eight at a time, and split and stored
-                    // afterwards: written as one loop (load, split, store, next chunk) the stores of one
-                    // chunk may alias the load of the next as far as the compiler can tell, and every
-                    // chunk paid a full shared-memory round trip — most of a narrow tile's k-block.
-                    constexpr int kPer = (kN4 + kWT - 1) / kWT;  // chunks per thread
-                    constexpr int kBatch = kPer < 8 ? kPer : 8;
-                    const bool tail_only = prec3 && p.trunc_hi;
-                    if (n4 != 0) {
-#pragma unroll
-                        for (int u0 = 0; u0 < kPer; u0 += kBatch) {
-                            float4 x[kBatch];
-#pragma unroll
-                            for (int u = 0; u < kBatch; ++u) {
-                                const int q = wtid + (u0 + u) * kWT;
-                                if (u0 + u < kPer && ((u0 + u + 1) * kWT <= kN4 || q < kN4)) x[u] = hi[q];
-                            }
-#pragma unroll
-                            for (int u = 0; u < kBatch; ++u) {
-                                const int q = wtid + (u0 + u) * kWT;
-                                if (u0 + u < kPer && ((u0 + u + 1) * kWT <= kN4 || q < kN4)) {
-                                    if (tail_only) {
-                                        // The raw tile stays as it is: the tensor core drops the low 13
-                                        // mantissa bits of what it reads, so its head is trunc(x); only the
-                                        // tail x - trunc(x) (exact in fp32, then rounded to TF32) is written —
-                                        // one pass of shared-memory stores instead of two.
-                                        lo[q] = make_float4(tf32_tail_of_truncated(x[u].x), tf32_tail_of_truncated(x[u].y),
-                                                            tf32_tail_of_truncated(x[u].z), tf32_tail_of_truncated(x[u].w));
-                                    } else {
-                                        float4 h, l;
-                                        tf32_split(x[u].x, h.x, l.x);
-                                        tf32_split(x[u].y, h.y, l.y);
-                                        tf32_split(x[u].z, h.z, l.z);
-                                        tf32_split(x[u].w, h.w, l.w);
-                                        hi[q] = h;
-                                        if (prec3) lo[q] = l;
-                                    }
-                                }
-                            }
-                        }
-                    }
+                    if (n4 != 0) split_stage<kN4, kWT, 8>(hi, lo, wtid, prec3, prec3 && p.trunc_hi);
                 } else {
                     bool got;
                     {
@@ -1188,10 +1244,12 @@ gemm_tf32_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA,
                     }
                     ldg_phase(std::false_type{}, std::true_type{}, wk, wk.kb0 + i, stage);
                 }
-                // generic-proxy writes -> visible to the tensor core's async-proxy reads
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) arrive_at_leader(smem_u32(&split_bar[s]));
+                if constexpr (kSW == 0) {
+                    // generic-proxy writes -> visible to the tensor core's async-proxy reads
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) arrive_at_leader(smem_u32(&split_bar[s]));
+                }
                 if constexpr (!kTma) {
                     // the next k-block's global loads fly while the accumulator is drained
                     if (i + 1 < nkb) ldg_phase(std::true_type{}, std::false_type{}, wk, wk.kb0 + i + 1, nullptr);

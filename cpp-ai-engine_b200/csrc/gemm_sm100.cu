@@ -54,6 +54,7 @@ struct Options {
     long pdl = 1;            // launch with programmatic stream serialization (set-up overlaps the previous kernel)
     long map_cache = 1;      // reuse encoded TMA tensor maps between calls
     long block_k = 0;        // values of k per pipeline stage: 0 = automatic, 32, or 64 (TMA loader, tiles up to 64 wide)
+    long split_warps = 0;    // pair kernel: 8 = eight more warps that only split, the workers only drain
     long pair_workers = 8;   // worker warps per CTA of the pair kernel: 8, or 16 (measured 3-5 % slower)
 };
 // Process-wide knobs, read without synchronisation on every call: set them while no other thread
@@ -299,13 +300,13 @@ int launch_cfg(const GemmParams& params, const CUtensorMap& ma, const CUtensorMa
 // warps per CTA (default) or sixteen (option "pair_workers"; twice the warps per scheduler, half the
 // accumulators each — bit-identical results, measured 3-5 % slower at 4096^3 ... 16384^3: the
 // workers' instruction latency is not what binds the kernel).
-template <int WW>
+template <int WW, int SW = 0>
 int max_pair_clusters_for(int dev) {
     static std::atomic<int> cached[kMaxDevices] = {};
     if (cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load(std::memory_order_relaxed);
     std::lock_guard<std::mutex> lock(g_mutex);
     using Cfg = TileCfg<256, 32, true, WW>;
-    auto kernel = gemm_tf32_kernel<256, 32, true, true, 0, WW>;
+    auto kernel = gemm_tf32_kernel<256, 32, true, true, 0, WW, SW>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::kSmemBytes)) != cudaSuccess) {
         cudaGetLastError();
@@ -313,7 +314,7 @@ int max_pair_clusters_for(int dev) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(Cfg::kThreadsCfg, 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreadsCfg + SW * 32, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -331,20 +332,22 @@ int max_pair_clusters_for(int dev) {
     return n;
 }
 int max_pair_clusters(int dev) {
+    if (g_opt.split_warps == 8) return max_pair_clusters_for<8, 8>(dev);
     return g_opt.pair_workers == 16 ? max_pair_clusters_for<16>(dev) : max_pair_clusters_for<8>(dev);
 }
 
-template <int WW>
+template <int WW, int SW = 0>
 int launch_pair_for(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
                     cudaStream_t stream) {
     using Cfg = TileCfg<256, 32, true, WW>;
     GemmParams p = params;
     fill_schedule(p);
-    return static_cast<int>(launch_kernel(gemm_tf32_kernel<256, 32, true, true, 0, WW>, 2 * clusters,
-                                          Cfg::kThreadsCfg, Cfg::kSmemBytes, stream, 2, p, ma, mb));
+    return static_cast<int>(launch_kernel(gemm_tf32_kernel<256, 32, true, true, 0, WW, SW>, 2 * clusters,
+                                          Cfg::kThreadsCfg + SW * 32, Cfg::kSmemBytes, stream, 2, p, ma, mb));
 }
 int launch_pair(const GemmParams& params, const CUtensorMap& ma, const CUtensorMap& mb, int clusters,
                 cudaStream_t stream) {
+    if (g_opt.split_warps == 8) return launch_pair_for<8, 8>(params, ma, mb, clusters, stream);
     return g_opt.pair_workers == 16 ? launch_pair_for<16>(params, ma, mb, clusters, stream)
                                     : launch_pair_for<8>(params, ma, mb, clusters, stream);
 }
@@ -1690,6 +1693,9 @@ int b200_gemm_set_option(const char* name, long value) {
     } else if (!std::strcmp(name, "block_k")) {
         if (value != 0 && value != 32 && value != 64) return B200_EINVAL;
         g_opt.block_k = value;
+    } else if (!std::strcmp(name, "split_warps")) {
+        if (value != 0 && value != 8) return B200_EINVAL;
+        g_opt.split_warps = value;
     } else if (!std::strcmp(name, "pair_workers")) {
         if (value != 8 && value != 16) return B200_EINVAL;
         g_opt.pair_workers = value;

@@ -423,6 +423,9 @@ uint64_t b200_gemm_launch_count(void);
  *                   k-loop; measured 3-5 % faster at K >= 384, slower at K = 96, error 1.2-1.6x: not the default)
  *   "pair_workers"  worker warps per CTA of the CTA-pair kernel: 8 (default) or 16 (same bits; measured 3-5 %
  *                   slower on a B200)
+ *   "split_warps"   CTA-pair kernel: 0 (default) = the eight worker warps split each landed stage and drain the
+ *                   accumulator in turn; 8 = eight more warps per CTA only split, the workers only drain and
+ *                   store (same bits; on a B200 1-2 % slower at 4096^3 and 8192^3, ~1 % faster at 16384^3)
  *   "pdl"           1 (default) = kernels are launched with programmatic stream serialization: the
  *                   set-up of a product overlaps the end of the kernel before it; 0 = plain launches
  *   "map_cache"     1 (default) = encoded TMA tensor maps are reused between calls with the same

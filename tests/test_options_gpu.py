@@ -24,9 +24,11 @@ def product(pkg, cuda, A, B, M, N, K, **kw):
     return C
 
 
-@pytest.mark.parametrize("workers", [16])
-def test_pair_kernel_with_sixteen_worker_warps_is_bit_identical(pkg, orc, cuda, workers):
-    """pair_workers = 16: half the accumulators per thread, twice the warps; the same sums in the same order."""
+@pytest.mark.parametrize("option,value,default", [("pair_workers", 16, 8), ("split_warps", 8, 0)])
+def test_pair_kernel_warp_layouts_are_bit_identical(pkg, orc, cuda, option, value, default):
+    """pair_workers = 16: half the accumulators per thread, twice the warps.  split_warps = 8: eight more
+    warps that only split the stages while the eight workers only drain and store.  The same sums in the
+    same order either way."""
     import torch
 
     g = orc.Rng(70)
@@ -35,11 +37,11 @@ def test_pair_kernel_with_sixteen_worker_warps_is_bit_identical(pkg, orc, cuda, 
         A, B = dev(a, cuda), dev(b, cuda)
         want = product(pkg, cuda, A, B, M, N, K, lda=K, ldb=N)
         assert pkg.plan(1, M, N, K)["pair"] == 1, "expected the CTA-pair kernel for this shape"
-        pkg.set_option("pair_workers", workers)
+        pkg.set_option(option, value)
         try:
             got = product(pkg, cuda, A, B, M, N, K, lda=K, ldb=N)
         finally:
-            pkg.set_option("pair_workers", 8)
+            pkg.set_option(option, default)
         assert torch.equal(got, want)
         rows = np.arange(0, M, 29)
         assert orc.scaled_error(got.cpu().numpy()[rows], orc.matmul(a[rows], b)) <= orc.parity_tolerance(K)
