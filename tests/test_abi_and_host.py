@@ -39,6 +39,27 @@ def test_error_strings_and_options(pkg):
     assert lib.b200_gemm_launch_count() >= 0
 
 
+def test_every_documented_option_is_accepted_and_the_list_is_complete(pkg):
+    """The option names listed under b200_gemm_set_option in the header are exactly the ones the library
+    accepts: each takes its default back, and a name the header does not list is refused."""
+    import re
+    from pathlib import Path
+
+    header = (Path(__file__).resolve().parents[1] / "include" / "b200_gemm.h").read_text()
+    block = header[: header.index("int b200_gemm_set_option(")]
+    block = block[block.rindex("/*"):]
+    documented = re.findall(r'^ \*   "([a-z_0-9]+)"', block, flags=re.M)
+    defaults = {"pair_workers": 8, "pdl": 1, "map_cache": 1, "host_pipeline": 1, "tail_split": 1, "tf32_round": 1}
+    lib = pkg.load()
+    assert len(documented) >= 14 and len(set(documented)) == len(documented)
+    for name in documented:
+        assert lib.b200_gemm_set_option(name.encode(), defaults.get(name, 0)) == 0, name
+    for name, bad in (("tile_n", 100), ("pair_mode", 3), ("head_mode", 2), ("block_k", 48), ("split_warps", 4),
+                      ("pair_workers", 12), ("split_k", -1), ("group_m", -1)):
+        assert name in documented
+        assert lib.b200_gemm_set_option(name.encode(), bad) == -1, name
+
+
 def test_no_cpu_fallback_without_device(pkg):
     """Without a CUDA device the entry points fail loudly instead of computing elsewhere."""
     import torch
