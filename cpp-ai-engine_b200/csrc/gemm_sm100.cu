@@ -30,7 +30,7 @@ struct DeviceState {
     void* stage_ws = nullptr;
     size_t cap_a = 0, cap_b = 0, cap_c = 0, cap_ws = 0;
     // streams and events of the pipelined host path (created on first use)
-    cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
+    cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_comp2 = nullptr, s_d2h = nullptr, s_d2h2 = nullptr;
     cudaEvent_t ev_a[16] = {}, ev_b[16] = {}, ev_c[256] = {};
     bool pipe_ready = false;
 };
@@ -863,18 +863,22 @@ int grow(void** ptr, size_t* cap, size_t need) {
 // are uploaded alternately (A_0, B_0, A_1, B_1, ...).  When B_k lands, the column strip
 // C(0..k, k) = A_0..k x B_k is multiplied as ONE product; when A_k lands, the row strip
 // C(k, 0..k-1) = A_k x B_0..k-1; each strip is downloaded as soon as it is done.  Uploads, kernels
-// and downloads run on three streams, so the bus works in both directions under the math.  Thin
+// and downloads run on streams of their own, so the bus works in both directions under the math.  Thin
 // panels keep the work that only the last pair of panels unlocks small while each strip is still
-// one large launch.  The uploads are the bound: 2 GiB at the 44 GB/s this host's PCIe link gives
-// while downloads run the other way take 49 of the ~56 ms of a 16384^3 product.  Overlap needs page-locked
-// host buffers; with pageable ones the copies serialise but the result is the same.
+// one large launch.  What can be multiplied grows with the square of what has been uploaded, so the
+// SMs idle ~10 ms early on and the math trails the uploads (2 GiB in 41 ms at 52 GB/s) at the end:
+// a 16384^3 product takes ~55 ms, close to T_math + T_upload^2 / (4 T_math), the best this order of
+// uploads allows.  Overlap needs page-locked host buffers; with pageable ones the copies serialise
+// but the result is the same.
 int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, int64_t M, int64_t K,
                    int64_t N) {
     cudaError_t e;
     if (!st.pipe_ready) {
         if ((e = cudaStreamCreateWithFlags(&st.s_h2d, cudaStreamNonBlocking)) != cudaSuccess) return e;
         if ((e = cudaStreamCreateWithFlags(&st.s_comp, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&st.s_comp2, cudaStreamNonBlocking)) != cudaSuccess) return e;
         if ((e = cudaStreamCreateWithFlags(&st.s_d2h, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&st.s_d2h2, cudaStreamNonBlocking)) != cudaSuccess) return e;
         for (auto& ev : st.ev_a)
             if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return e;
         for (auto& ev : st.ev_b)
@@ -912,22 +916,28 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
                                             static_cast<size_t>(K), cudaMemcpyHostToDevice, st.s_h2d);
         return err != cudaSuccess ? err : cudaEventRecord(st.ev_b[j], st.s_h2d);
     };
-    // C[r0 : r0 + rows, c0 : c0 + cols], once the uploads recorded in `ready` have landed
+    // C[r0 : r0 + rows, c0 : c0 + cols], once the uploads recorded in `ready` have landed.  The strips
+    // are independent products (disjoint parts of C, no scratch), so they alternate between two
+    // pairs of a compute and a download stream: a strip's persistent CTAs that find no tile left in
+    // its last wave exit and the next strip's CTAs start on those SMs instead of waiting for the whole
+    // launch to end, and a strip's download queues behind its own stream's strips only.
     int strips = 0;
     auto strip = [&](int64_t r0, int64_t rows, int64_t c0, int64_t cols, cudaEvent_t ready) -> int {
         if (rows <= 0 || cols <= 0) return 0;
         cudaError_t err;
-        if ((err = cudaStreamWaitEvent(st.s_comp, ready, 0)) != cudaSuccess) return err;
+        cudaStream_t comp = (strips & 1) ? st.s_comp2 : st.s_comp;
+        cudaStream_t down = (strips & 1) ? st.s_d2h2 : st.s_d2h;
+        if ((err = cudaStreamWaitEvent(comp, ready, 0)) != cudaSuccess) return err;
         float* dest[1] = {dC + r0 * N + c0};
         int rc = gemm_impl(st, dA + r0 * K, dB + c0, dest, 1, 1, rows, cols, K, 0, 0, K, N, N, 0, 0,
-                           rows * N, 1.0f, 0.0f, B200_PRECISION_3XTF32, nullptr, 0, st.s_comp);
+                           rows * N, 1.0f, 0.0f, B200_PRECISION_3XTF32, nullptr, 0, comp);
         if (rc) return rc;
         cudaEvent_t done = st.ev_c[strips++];
-        if ((err = cudaEventRecord(done, st.s_comp)) != cudaSuccess) return err;
-        if ((err = cudaStreamWaitEvent(st.s_d2h, done, 0)) != cudaSuccess) return err;
+        if ((err = cudaEventRecord(done, comp)) != cudaSuccess) return err;
+        if ((err = cudaStreamWaitEvent(down, done, 0)) != cudaSuccess) return err;
         err = cudaMemcpy2DAsync(out + r0 * N + c0, static_cast<size_t>(N) * 4, dC + r0 * N + c0,
                                 static_cast<size_t>(N) * 4, static_cast<size_t>(cols) * 4,
-                                static_cast<size_t>(rows), cudaMemcpyDeviceToHost, st.s_d2h);
+                                static_cast<size_t>(rows), cudaMemcpyDeviceToHost, down);
         return err;
     };
 
@@ -951,7 +961,9 @@ int host_wavefront(DeviceState& st, const float* a, const float* b, float* out, 
     }
     if ((e = cudaStreamSynchronize(st.s_h2d)) != cudaSuccess) return e;
     if ((e = cudaStreamSynchronize(st.s_comp)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(st.s_comp2)) != cudaSuccess) return e;
     if ((e = cudaStreamSynchronize(st.s_d2h)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(st.s_d2h2)) != cudaSuccess) return e;
     return B200_OK;
 }
 
@@ -1081,7 +1093,9 @@ int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batc
             // leave no copy from or to the caller's buffers in flight behind an error return
             cudaStreamSynchronize(st->s_h2d);
             cudaStreamSynchronize(st->s_comp);
+            cudaStreamSynchronize(st->s_comp2);
             cudaStreamSynchronize(st->s_d2h);
+            cudaStreamSynchronize(st->s_d2h2);
         }
         return rc;
     }
