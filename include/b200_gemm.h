@@ -249,7 +249,7 @@ int b200_matmul_f32(const float* a, const float* b, float* out, size_t batch, si
  * the reference's Storage uploads stale operands and a later data() downloads the result
  * (src/storage.cpp:281-307).  Device staging buffers are cached per device between calls.
  * A large single product (rows, cols >= 4096) is run as a wavefront of blocks whose uploads,
- * kernels and downloads overlap on three streams; pass page-locked host buffers to get the
+ * kernels and downloads overlap on streams of their own; pass page-locked host buffers to get the
  * overlap (pageable ones work, serialised). */
 int b200_matmul_f32_host(const float* a, const float* b, float* out, size_t batch, size_t rows,
                          size_t inner_dim, size_t cols, int a_batched, int b_batched, float beta);
